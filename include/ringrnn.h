@@ -1,0 +1,183 @@
+/* ringrnn.h -- C ABI of libringrnn.so: the ring-attractor recurrent forward and
+ * backward-through-time operator for NVIDIA B200 (sm_100a).
+ *
+ * Plain pointers and sizes only; every pointer named "device" is CUDA device memory owned by
+ * the caller, including all scratch ("workspace") and saved-for-backward storage, whose sizes
+ * ringrnn_workspace_bytes() reports.  No entry point allocates device memory, exits the process
+ * or throws: each returns a RINGRNN_* status.  Calls are asynchronous on `stream` (a cudaStream_t
+ * passed as void*; NULL = the legacy default stream) and may come from any host thread.
+ *
+ * Each declaration cites the interface of the reference project (chongxi/rnn_train_ring_attractor,
+ * paths relative to its root) that it replaces.
+ */
+#ifndef RINGRNN_H
+#define RINGRNN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+enum {
+  RINGRNN_OK = 0,
+  RINGRNN_ERR_ARG = 1,         /* NULL where a pointer is required, bad enum value            */
+  RINGRNN_ERR_SHAPE = 2,       /* non-positive or unsupported dimension                        */
+  RINGRNN_ERR_WORKSPACE = 3,   /* workspace / saved buffer missing, misaligned or too small    */
+  RINGRNN_ERR_CUDA = 4,        /* a CUDA runtime call failed (see ringrnn_last_cuda_error)     */
+  RINGRNN_ERR_UNSUPPORTED = 5, /* valid request that this precision mode cannot serve          */
+  RINGRNN_ERR_DEVICE = 6       /* a kernel reported a bounded wait that ran out                */
+};
+
+/* activation codes: the enum order of cpp/cuda_common.cuh:56 and the activation_map of
+ * cpp/ring_rnn_cuda.py:63 */
+enum { RINGRNN_ACT_RELU = 0, RINGRNN_ACT_GELU = 1, RINGRNN_ACT_TANH = 2, RINGRNN_ACT_SILU = 3 };
+
+/* arithmetic mode.  FP32: CUDA-core FFMA throughout (the reference's fwd_fp32 path,
+ * cpp/kernels/fwd_fp32.cuh).  BF16: bf16 tensor-core operands with fp32 accumulation and an fp32
+ * master state (the reference's WMMA path, cpp/kernels/fwd_1loop_tc_idx.cuh). */
+enum { RINGRNN_PREC_FP32 = 0, RINGRNN_PREC_BF16 = 1 };
+
+/* which buffer ringrnn_workspace_bytes() sizes */
+enum { RINGRNN_WS_FWD = 0, RINGRNN_WS_SAVED = 1, RINGRNN_WS_BWD = 2 };
+
+#define RINGRNN_MAX_ACTIVE 64
+
+/* The problem both directions share.  Tensor arguments follow cpp/fwd.cu:5-19:
+ *   A[B,T,a_dim], Wa[a_dim,N,N], Wo[N,N], r_init[B,N], all fp32, contiguous, device memory.
+ * n_active / active_cols name the columns of A that are not identically zero (the root training
+ * script pads the L/R signal to 16 columns with zeros, train_general_ring_no_gain.py:200-223);
+ * n_active < 0 means "all a_dim columns".  Gradients of skipped columns are exactly zero. */
+typedef struct RingRnnProblem {
+  int B, T, N, a_dim;
+  int activation; /* RINGRNN_ACT_*  */
+  int precision;  /* RINGRNN_PREC_* */
+  float J0, J1, alpha;
+  const float* A;
+  const float* Wa;
+  const float* Wo;
+  const float* r_init;
+  int n_active;
+  int active_cols[RINGRNN_MAX_ACTIVE];
+} RingRnnProblem;
+
+/* Forward.  Replaces fwd_cuda() (cpp/fwd.cu:21-50) and its launchers
+ * (cpp/kernels/fwd_1loop_tc_idx.cuh:280-311, cpp/kernels/fwd_fp32.cuh:277-298).
+ *   bump_history  [T,B,N] fp32 out, layout of cpp/ring_rnn_cuda.py:62; NULL = do not write the history
+ *   saved         storage the backward call needs (RINGRNN_WS_SAVED bytes); NULL = inference
+ *   dec_x, dec_y  [B,T] fp32 out: population-vector components r_t.u and r_t.v (NULL = skip)
+ *   dec_ta        [B,T] fp32 out: sum_i |r_t[b,i]|                              (NULL = skip)
+ *   dec_u, dec_v  [N] fp32 in, required when any dec_* output is requested
+ *   final_state   [B,N] fp32 out, r_T (NULL = skip)
+ *   workspace     RINGRNN_WS_FWD bytes of scratch
+ *   status        optional device int, set non-zero if a bounded device-side wait ran out */
+typedef struct RingRnnFwdArgs {
+  RingRnnProblem p;
+  float* bump_history;
+  void* saved;
+  size_t saved_bytes;
+  float* dec_x;
+  float* dec_y;
+  float* dec_ta;
+  const float* dec_u;
+  const float* dec_v;
+  float* final_state;
+  void* workspace;
+  size_t workspace_bytes;
+  int* status;
+} RingRnnFwdArgs;
+
+/* Backward through time.  Replaces bwd_cuda() (cpp/bwd.cu:4-52) and
+ * bwd_wmma_launcher (cpp/kernels/bwd_mixed_precision_aggressive.cuh:676-707).
+ * The cotangent of the history is the sum of two optional sources:
+ *   grad_output [T,B,N] fp32 (cpp/ring_rnn_cuda.py:88), and
+ *   coef_x, coef_y, coef_s [B,T] fp32 with dec_u, dec_v [N]:
+ *     g_t[b,i] += coef_x[b,t]*u[i] + coef_y[b,t]*v[i] + coef_s[b,t]*sign(r_t[b,i])
+ *   (the closed-form gradient of the decode + cosine + bump-amplitude loss).
+ *   bump_history  the forward output when it was written; NULL = use `saved`
+ *   grad_Wa [a_dim,N,N], grad_Wo [N,N]  fp32 out, overwritten (cpp/ring_rnn_cuda.py:98-99, :144)
+ *   grad_J        float[2] out = {dL/dJ0, dL/dJ1}, NULL = skip (the reference returns None)
+ *   grad_r_init   [B,N] out, NULL = skip (the reference returns None) */
+typedef struct RingRnnBwdArgs {
+  RingRnnProblem p;
+  const float* grad_output;
+  const float* coef_x;
+  const float* coef_y;
+  const float* coef_s;
+  const float* dec_u;
+  const float* dec_v;
+  const float* bump_history;
+  const void* saved;
+  size_t saved_bytes;
+  float* grad_Wa;
+  float* grad_Wo;
+  float* grad_J;
+  float* grad_r_init;
+  void* workspace;
+  size_t workspace_bytes;
+  int* status;
+} RingRnnBwdArgs;
+
+/* library version (major*10000 + minor*100 + patch) */
+int ringrnn_version(void);
+
+/* text for a RINGRNN_* status.  Replaces the print-and-exit of CHECK_CUDA_ERROR
+ * (cpp/cuda_common.cuh:30-39): errors are returned, never fatal. */
+const char* ringrnn_strerror(int status);
+
+/* cudaError_t of the most recent failing CUDA call on this host thread (0 if none) and its text */
+int ringrnn_last_cuda_error(void);
+const char* ringrnn_last_cuda_error_string(void);
+
+/* Bytes of RINGRNN_WS_FWD / _SAVED / _BWD storage for a problem.  `history_given` says whether the
+ * caller keeps bump_history itself (then the fp32 mode saves nothing).  Replaces the per-call
+ * torch allocations of cpp/ring_rnn_cuda.py:105-114 and the cudaMalloc/cudaFree inside
+ * cpp/kernels/fwd_fp32.cuh:246-274.  Returns (size_t)-1 for an invalid problem. */
+size_t ringrnn_workspace_bytes(const RingRnnProblem* p, int which, int history_given);
+
+int ringrnn_fwd(const RingRnnFwdArgs* args, void* stream);
+int ringrnn_bwd(const RingRnnBwdArgs* args, void* stream);
+
+/* The reference's own native signatures with a status return, an explicit precision, caller
+ * scratch and a stream appended.  Argument meaning as cpp/fwd.cu:5-19 and cpp/bwd.cu:4-30; the
+ * reference's bwd scratch tensors (grad_r, W_eff_temp, ...) and cuBLAS handle are not needed. */
+int ringrnn_fwd_cuda(const void* A, const void* Wa, float J0, float J1, const void* Wo, const void* r_init,
+                     void* bump_history, float alpha, int N, int a_dim, int seq_len, int batch_size,
+                     int activation_type, int precision, void* saved, size_t saved_bytes, void* workspace,
+                     size_t workspace_bytes, void* stream);
+int ringrnn_bwd_cuda(const void* grad_output, const void* A, const void* Wa, float J0, float J1, const void* Wo,
+                     const void* bump_history, const void* r_init, void* grad_Wa, void* grad_Wo, float alpha,
+                     int N, int a_dim, int seq_len, int batch_size, int activation_type, int precision,
+                     const void* saved, size_t saved_bytes, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Decode + loss on the [B,T] scalars the forward emits.  Replaces the [B,T,N]-sized chain
+ * `bump @ W_delta7`, max-normalise (train_general_ring_no_gain.py:113-116), cosine_similarity_loss
+ * (train/train_ring_attractor.py:190-220) and bump_amplitude_loss (:275-298).
+ *   target  [B,T] true angle;  inv_count = 1/(B_global*T);  bump_weight = 0.2 in the reference
+ *   coef_x/y/s [B,T] out (inputs of ringrnn_bwd);  decoded [B,T] out in [0,2pi), NULL = skip
+ *   loss_out  float[2] out = {sum of (2-2cos(err)) * inv_count, sum of amplitude deviations^2 * inv_count}
+ *   scratch   B floats * 2 */
+int ringrnn_angle_loss(int B, int T, const float* dec_x, const float* dec_y, const float* dec_ta,
+                       const float* target, float bump_weight, float inv_count, float* coef_x, float* coef_y,
+                       float* coef_s, float* decoded, float* loss_out, float* scratch, void* stream);
+
+/* Launch accounting and per-kernel timing (the reference's counterpart is the NVTX / cudaProfiler
+ * bracketing in legacy/bwd_fp32.py:705-740 and utils/benchmark.py:58-79).
+ *   ringrnn_launch_count   kernels launched by this library since the last reset
+ *   ringrnn_timing_enable  when on, every kernel launch is bracketed by a CUDA event pair on its stream
+ *   ringrnn_timing_read    synchronises the recorded events and returns, for kernel class `slot`
+ *                          (0 <= slot < ringrnn_timing_slots()), the summed milliseconds and launch count
+ *   ringrnn_timing_reset   drops recorded events and zeroes the counters */
+long long ringrnn_launch_count(void);
+int ringrnn_timing_slots(void);
+const char* ringrnn_timing_name(int slot);
+int ringrnn_timing_enable(int on);
+int ringrnn_timing_read(int slot, float* total_ms, int* launches);
+int ringrnn_timing_reset(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RINGRNN_H */

@@ -1,0 +1,219 @@
+// extern "C" surface of libringrnn.so: argument checking, precision dispatch, error reporting.
+#include <string.h>
+
+#include <atomic>
+#include <mutex>
+#include <vector>
+
+#include "ringrnn_common.cuh"
+
+namespace ringrnn {
+
+static thread_local cudaError_t g_last_cuda_error = cudaSuccess;
+void set_last_cuda_error(cudaError_t e) { g_last_cuda_error = e; }
+
+// ---- launch accounting ---------------------------------------------------------------------
+static std::atomic<long long> g_launches{0};
+static std::atomic<int> g_timing_on{0};
+static std::mutex g_timing_mu;
+struct TimedLaunch { int slot; cudaEvent_t start, stop; };
+static std::vector<TimedLaunch> g_timed;
+static float g_slot_ms[K_SLOTS];
+static int g_slot_n[K_SLOTS];
+
+LaunchScope::LaunchScope(int slot, cudaStream_t s) : slot_(slot), s_(s), start_(nullptr), timed_(false) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (g_timing_on.load(std::memory_order_relaxed)) {
+    if (cudaEventCreate(&start_) == cudaSuccess) {
+      cudaEventRecord(start_, s_);
+      timed_ = true;
+    }
+  }
+}
+LaunchScope::~LaunchScope() {
+  if (!timed_) return;
+  cudaEvent_t stop;
+  if (cudaEventCreate(&stop) != cudaSuccess) { cudaEventDestroy(start_); return; }
+  cudaEventRecord(stop, s_);
+  std::lock_guard<std::mutex> lk(g_timing_mu);
+  g_timed.push_back({slot_, start_, stop});
+}
+
+static void drain_timed_locked() {
+  for (auto& t : g_timed) {
+    float ms = 0.f;
+    if (cudaEventSynchronize(t.stop) == cudaSuccess && cudaEventElapsedTime(&ms, t.start, t.stop) == cudaSuccess) {
+      g_slot_ms[t.slot] += ms;
+      g_slot_n[t.slot] += 1;
+    }
+    cudaEventDestroy(t.start);
+    cudaEventDestroy(t.stop);
+  }
+  g_timed.clear();
+}
+
+namespace {
+
+int check_problem(const RingRnnProblem& p) {
+  if (p.B <= 0 || p.T <= 0 || p.N <= 0 || p.a_dim <= 0) return RINGRNN_ERR_SHAPE;
+  if (p.activation < RINGRNN_ACT_RELU || p.activation > RINGRNN_ACT_SILU) return RINGRNN_ERR_ARG;
+  if (p.precision != RINGRNN_PREC_FP32 && p.precision != RINGRNN_PREC_BF16) return RINGRNN_ERR_ARG;
+  if (p.n_active > p.a_dim || p.n_active > RINGRNN_MAX_ACTIVE) return RINGRNN_ERR_ARG;
+  if (p.n_active < 0 && p.a_dim > RINGRNN_MAX_ACTIVE) return RINGRNN_ERR_UNSUPPORTED;
+  for (int k = 0; k < p.n_active; ++k)
+    if (p.active_cols[k] < 0 || p.active_cols[k] >= p.a_dim) return RINGRNN_ERR_ARG;
+  return RINGRNN_OK;
+}
+
+int check_pointers(const RingRnnProblem& p) {
+  if (!p.A || !p.Wa || !p.Wo || !p.r_init) return RINGRNN_ERR_ARG;
+  return RINGRNN_OK;
+}
+
+DevProblem to_dev(const RingRnnProblem& p) {
+  DevProblem d;
+  memset(&d, 0, sizeof(d));
+  d.B = p.B; d.T = p.T; d.N = p.N; d.a_dim = p.a_dim;
+  d.J0 = p.J0; d.J1 = p.J1; d.alpha = p.alpha;
+  d.A = p.A; d.Wa = p.Wa; d.Wo = p.Wo; d.r_init = p.r_init;
+  const int n = (p.n_active < 0) ? p.a_dim : p.n_active;
+  d.n_mat = 1 + n;
+  for (int k = 0; k < n; ++k) d.cols[k] = (p.n_active < 0) ? k : p.active_cols[k];
+  return d;
+}
+
+}  // namespace
+}  // namespace ringrnn
+
+using namespace ringrnn;
+
+extern "C" int ringrnn_version(void) { return 100; }
+
+extern "C" const char* ringrnn_strerror(int status) {
+  switch (status) {
+    case RINGRNN_OK: return "ok";
+    case RINGRNN_ERR_ARG: return "invalid argument (null pointer or bad enum value)";
+    case RINGRNN_ERR_SHAPE: return "invalid or unsupported shape";
+    case RINGRNN_ERR_WORKSPACE: return "workspace or saved buffer missing or too small";
+    case RINGRNN_ERR_CUDA: return "CUDA runtime error";
+    case RINGRNN_ERR_UNSUPPORTED: return "request not supported by this precision mode";
+    case RINGRNN_ERR_DEVICE: return "a bounded device-side wait ran out";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int ringrnn_last_cuda_error(void) { return (int)g_last_cuda_error; }
+extern "C" const char* ringrnn_last_cuda_error_string(void) { return cudaGetErrorString(g_last_cuda_error); }
+
+extern "C" size_t ringrnn_workspace_bytes(const RingRnnProblem* p, int which, int history_given) {
+  if (p == nullptr || check_problem(*p) != RINGRNN_OK) return (size_t)-1;
+  const bool bf16 = p->precision == RINGRNN_PREC_BF16;
+  if (bf16 && !bf16_supported(*p)) return (size_t)-1;
+  switch (which) {
+    case RINGRNN_WS_FWD: return bf16 ? bf16_fwd_workspace_bytes(*p) : fp32_fwd_workspace_bytes(*p);
+    case RINGRNN_WS_SAVED: return bf16 ? bf16_saved_bytes(*p) : fp32_saved_bytes(*p, history_given);
+    case RINGRNN_WS_BWD: return bf16 ? bf16_bwd_workspace_bytes(*p) : fp32_bwd_workspace_bytes(*p);
+    default: return (size_t)-1;
+  }
+}
+
+extern "C" int ringrnn_fwd(const RingRnnFwdArgs* a, void* stream) {
+  if (a == nullptr) return RINGRNN_ERR_ARG;
+  int rc = check_problem(a->p);
+  if (rc != RINGRNN_OK) return rc;
+  rc = check_pointers(a->p);
+  if (rc != RINGRNN_OK) return rc;
+  const bool want_dec = a->dec_x || a->dec_y || a->dec_ta;
+  if (want_dec && (!a->dec_u || !a->dec_v)) return RINGRNN_ERR_ARG;
+  if (!a->bump_history && !a->saved && !want_dec && !a->final_state) return RINGRNN_ERR_ARG;  // nothing to produce
+  const DevProblem dp = to_dev(a->p);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (a->p.precision == RINGRNN_PREC_BF16) {
+    if (!bf16_supported(a->p)) return RINGRNN_ERR_UNSUPPORTED;
+    return bf16_forward(*a, dp, s);
+  }
+  return fp32_forward(*a, dp, s);
+}
+
+extern "C" int ringrnn_bwd(const RingRnnBwdArgs* a, void* stream) {
+  if (a == nullptr) return RINGRNN_ERR_ARG;
+  int rc = check_problem(a->p);
+  if (rc != RINGRNN_OK) return rc;
+  rc = check_pointers(a->p);
+  if (rc != RINGRNN_OK) return rc;
+  if (!a->grad_Wa || !a->grad_Wo) return RINGRNN_ERR_ARG;
+  if (!a->grad_output && !a->coef_x) return RINGRNN_ERR_ARG;
+  if (a->coef_x && (!a->coef_y || !a->coef_s || !a->dec_u || !a->dec_v)) return RINGRNN_ERR_ARG;
+  const DevProblem dp = to_dev(a->p);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (a->p.precision == RINGRNN_PREC_BF16) {
+    if (!bf16_supported(a->p)) return RINGRNN_ERR_UNSUPPORTED;
+    return bf16_backward(*a, dp, s);
+  }
+  return fp32_backward(*a, dp, s);
+}
+
+extern "C" int ringrnn_fwd_cuda(const void* A, const void* Wa, float J0, float J1, const void* Wo,
+                                const void* r_init, void* bump_history, float alpha, int N, int a_dim, int seq_len,
+                                int batch_size, int activation_type, int precision, void* saved, size_t saved_bytes,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  RingRnnFwdArgs a;
+  memset(&a, 0, sizeof(a));
+  a.p.B = batch_size; a.p.T = seq_len; a.p.N = N; a.p.a_dim = a_dim;
+  a.p.activation = activation_type; a.p.precision = precision;
+  a.p.J0 = J0; a.p.J1 = J1; a.p.alpha = alpha;
+  a.p.A = static_cast<const float*>(A); a.p.Wa = static_cast<const float*>(Wa);
+  a.p.Wo = static_cast<const float*>(Wo); a.p.r_init = static_cast<const float*>(r_init);
+  a.p.n_active = -1;
+  a.bump_history = static_cast<float*>(bump_history);
+  a.saved = saved; a.saved_bytes = saved_bytes;
+  a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+  return ringrnn_fwd(&a, stream);
+}
+
+extern "C" int ringrnn_bwd_cuda(const void* grad_output, const void* A, const void* Wa, float J0, float J1,
+                                const void* Wo, const void* bump_history, const void* r_init, void* grad_Wa,
+                                void* grad_Wo, float alpha, int N, int a_dim, int seq_len, int batch_size,
+                                int activation_type, int precision, const void* saved, size_t saved_bytes,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  RingRnnBwdArgs a;
+  memset(&a, 0, sizeof(a));
+  a.p.B = batch_size; a.p.T = seq_len; a.p.N = N; a.p.a_dim = a_dim;
+  a.p.activation = activation_type; a.p.precision = precision;
+  a.p.J0 = J0; a.p.J1 = J1; a.p.alpha = alpha;
+  a.p.A = static_cast<const float*>(A); a.p.Wa = static_cast<const float*>(Wa);
+  a.p.Wo = static_cast<const float*>(Wo); a.p.r_init = static_cast<const float*>(r_init);
+  a.p.n_active = -1;
+  a.grad_output = static_cast<const float*>(grad_output);
+  a.bump_history = static_cast<const float*>(bump_history);
+  a.saved = saved; a.saved_bytes = saved_bytes;
+  a.grad_Wa = static_cast<float*>(grad_Wa); a.grad_Wo = static_cast<float*>(grad_Wo);
+  a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+  return ringrnn_bwd(&a, stream);
+}
+
+extern "C" long long ringrnn_launch_count(void) { return g_launches.load(); }
+extern "C" int ringrnn_timing_slots(void) { return K_SLOTS; }
+extern "C" const char* ringrnn_timing_name(int slot) {
+  static const char* names[K_SLOTS] = {"prep", "fwd_recurrent", "bwd_recurrent", "dw_product", "dw_reduce", "loss"};
+  return (slot >= 0 && slot < K_SLOTS) ? names[slot] : "";
+}
+extern "C" int ringrnn_timing_enable(int on) {
+  g_timing_on.store(on ? 1 : 0);
+  return RINGRNN_OK;
+}
+extern "C" int ringrnn_timing_read(int slot, float* total_ms, int* launches) {
+  if (slot < 0 || slot >= K_SLOTS || !total_ms || !launches) return RINGRNN_ERR_ARG;
+  std::lock_guard<std::mutex> lk(g_timing_mu);
+  drain_timed_locked();
+  *total_ms = g_slot_ms[slot];
+  *launches = g_slot_n[slot];
+  return RINGRNN_OK;
+}
+extern "C" int ringrnn_timing_reset(void) {
+  std::lock_guard<std::mutex> lk(g_timing_mu);
+  drain_timed_locked();
+  for (int i = 0; i < K_SLOTS; ++i) { g_slot_ms[i] = 0.f; g_slot_n[i] = 0; }
+  g_launches.store(0);
+  return RINGRNN_OK;
+}

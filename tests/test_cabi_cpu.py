@@ -1,0 +1,118 @@
+"""Host-side checks that need no GPU: the C-ABI library loads, exports everything include/ringrnn.h
+declares, validates arguments before touching CUDA, and sizes its buffers sanely."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from rnn_train_ring_attractor_b200 import _lib
+from rnn_train_ring_attractor_b200.build import build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def L():
+    build()
+    return _lib.lib()
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "ringrnn.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ringrnn_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_all_exported(L):
+    names = declared_functions()
+    assert "ringrnn_fwd" in names and "ringrnn_bwd" in names and len(names) >= 9
+    for n in names:
+        assert hasattr(L, n), f"{n} declared in include/ringrnn.h but not exported"
+    assert sorted(_lib.SYMBOLS) == names, "ctypes table and header disagree"
+
+
+def test_version_and_strerror(L):
+    assert L.ringrnn_version() >= 100
+    assert L.ringrnn_strerror(0) == b"ok"
+    for code in range(1, 7):
+        assert len(L.ringrnn_strerror(code)) > 3
+    assert L.ringrnn_strerror(99) == b"unknown status"
+
+
+def _problem(**kw):
+    d = dict(B=8, T=5, N=24, a_dim=2, act=2, prec=0, J0=-0.1, J1=0.1, alpha=0.1, A=1, Wa=1, Wo=1, r_init=1)
+    d.update(kw)
+    return _lib.make_problem(d["B"], d["T"], d["N"], d["a_dim"], d["act"], d["prec"], d["J0"], d["J1"], d["alpha"],
+                             d["A"], d["Wa"], d["Wo"], d["r_init"], d.get("active"))
+
+
+def test_argument_validation_returns_status_not_exit(L):
+    assert L.ringrnn_fwd(None, None) == 1
+    assert L.ringrnn_bwd(None, None) == 1
+    a = _lib.FwdArgs()
+    a.p = _problem(B=0)
+    assert L.ringrnn_fwd(C.byref(a), None) == 2  # shape
+    a.p = _problem(act=7)
+    assert L.ringrnn_fwd(C.byref(a), None) == 1  # bad activation code
+    a.p = _problem(A=None)
+    assert L.ringrnn_fwd(C.byref(a), None) == 1  # null tensor
+    a.p = _problem()
+    assert L.ringrnn_fwd(C.byref(a), None) == 1  # nothing to produce
+    a.bump_history = 1
+    assert L.ringrnn_fwd(C.byref(a), None) == 3  # no workspace
+    b = _lib.BwdArgs()
+    b.p = _problem()
+    assert L.ringrnn_bwd(C.byref(b), None) == 1  # no grad outputs
+    b.grad_Wa, b.grad_Wo = 1, 1
+    assert L.ringrnn_bwd(C.byref(b), None) == 1  # no cotangent source
+    b.grad_output = 1
+    b.bump_history = 1
+    assert L.ringrnn_bwd(C.byref(b), None) == 3  # no workspace
+    a.p = _problem(active=[0, 5])
+    assert L.ringrnn_fwd(C.byref(a), None) == 1  # active column out of range
+    assert L.ringrnn_angle_loss(0, 4, 1, 1, 1, 1, 0.2, 1.0, 1, 1, 1, None, 1, 1, None) == 2
+    assert L.ringrnn_angle_loss(4, 4, None, 1, 1, 1, 0.2, 1.0, 1, 1, 1, None, 1, 1, None) == 1
+
+
+def test_workspace_sizes(L):
+    p = _problem(B=128, T=120, N=120)
+    fwd = L.ringrnn_workspace_bytes(C.byref(p), _lib.WS_FWD, 1)
+    assert fwd >= 3 * 120 * 120 * 4
+    assert L.ringrnn_workspace_bytes(C.byref(p), _lib.WS_SAVED, 1) == 0
+    assert L.ringrnn_workspace_bytes(C.byref(p), _lib.WS_SAVED, 0) >= 120 * 128 * 120 * 4
+    bwd = L.ringrnn_workspace_bytes(C.byref(p), _lib.WS_BWD, 1)
+    assert bwd >= 120 * 128 * 120 * 4 + 3 * 120 * 120 * 4
+    bad = _problem(N=-3)
+    assert L.ringrnn_workspace_bytes(C.byref(bad), _lib.WS_FWD, 1) == C.c_size_t(-1).value
+    assert L.ringrnn_workspace_bytes(None, _lib.WS_FWD, 1) == C.c_size_t(-1).value
+    assert L.ringrnn_workspace_bytes(C.byref(p), 9, 1) == C.c_size_t(-1).value
+    pa = _problem(a_dim=16, active=[0, 1])
+    pf = _problem(a_dim=16)
+    assert L.ringrnn_workspace_bytes(C.byref(pa), _lib.WS_FWD, 1) < L.ringrnn_workspace_bytes(C.byref(pf), _lib.WS_FWD, 1)
+
+
+def test_python_surface_mirrors_reference_names():
+    import cpp.ring_rnn_cuda as m
+    import cpp.rnn_cuda as r
+    assert hasattr(m, "torch") and hasattr(m, "Function")  # leak through the star import, as the reference
+    assert not hasattr(m, "__all__")
+    assert callable(m.ring_rnn_cuda_func) and issubclass(m.RingRnnCudaFunc, m.Function)
+    assert hasattr(r.fwd_cuda, "fwd") and hasattr(r.bwd_cuda, "bwd")
+    import inspect
+    sig = inspect.signature(m.ring_rnn_cuda_func)
+    assert list(sig.parameters) == ["action_signal", "Wa", "J0", "J1", "Wo", "r_init", "alpha", "activation"]
+    assert sig.parameters["activation"].default == "relu"
+
+
+def test_operator_refuses_cpu_tensors_loudly():
+    import torch
+    import cpp.ring_rnn_cuda as m
+    A = torch.zeros(2, 3, 2)
+    Wa = torch.zeros(2, 4, 4)
+    Wo = torch.zeros(4, 4)
+    r0 = torch.zeros(2, 4)
+    with pytest.raises(ValueError):
+        m.ring_rnn_cuda_func(A, Wa, -0.1, 0.1, Wo, r0, 0.1, "swish")
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        m.ring_rnn_cuda_func(A, Wa, -0.1, 0.1, Wo, r0, 0.1, "tanh")

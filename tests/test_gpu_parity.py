@@ -1,0 +1,285 @@
+"""CUDA path vs the CPU oracle, through the C ABI (ringrnn_fwd / ringrnn_bwd / ringrnn_angle_loss).
+
+Tolerances (rel = ||x - ref||_F / ||ref||_F, see oracle.ring_oracle.rel_err):
+  fp32 mode: 1e-4 on history, loss and every gradient;  bf16 mode: 1e-2.
+Edge cases follow what the reference's dispatch distinguishes (cpp/fwd.cu:36): sizes that are and are not
+multiples of 16, a single sample, a single step, zero-padded action columns (a_dim=16), generic action
+columns (a_dim=4), every activation.
+"""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ring_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"fp32": 1e-4, "bf16": 1e-2}
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _dev(*ts):
+    return [t.cuda().contiguous() for t in ts]
+
+
+def random_case(N, B, T, a_dim, act, seed, alpha=0.1, scale=None, pad_cols=False):
+    g = torch.Generator().manual_seed(seed)
+    scale = scale if scale is not None else 1.0 / math.sqrt(N)
+    Wo = torch.randn(N, N, generator=g) * scale
+    Wa = torch.randn(a_dim, N, N, generator=g) * scale
+    A = torch.rand(B, T, a_dim, generator=g) * 0.3
+    if pad_cols:
+        A[:, :, 2:] = 0.0
+    r0 = torch.rand(B, N, generator=g)
+    return A, Wa, Wo, r0, -0.1, 0.1, alpha, act
+
+
+FWD_SHAPES = [
+    # N, B, T, a_dim, act, pad_cols
+    (16, 1, 1, 2, "relu", False),
+    (16, 7, 2, 2, "tanh", False),
+    (120, 128, 120, 2, "tanh", False),   # the CPU-runnable benchmark config
+    (120, 130, 65, 2, "gelu", False),
+    (128, 128, 65, 2, "silu", False),
+    (256, 130, 20, 16, "gelu", True),    # zero-padded action columns, as the root training script
+    (40, 33, 17, 4, "relu", False),      # generic action columns
+    (256, 7, 9, 2, "tanh", False),
+    (512, 16, 5, 2, "gelu", False),
+]
+
+
+def _modes_for(N, B, T, a_dim, n_active):
+    import ctypes as C
+    from rnn_train_ring_attractor_b200 import _lib
+    modes = ["fp32"]
+    p = _lib.make_problem(B, T, N, a_dim, 0, 1, 0, 0, 0, 1, 1, 1, 1, list(range(n_active)))
+    if _lib.lib().ringrnn_workspace_bytes(C.byref(p), 0, 1) != C.c_size_t(-1).value:
+        modes.append("bf16")
+    return modes
+
+
+@pytest.mark.parametrize("shape", FWD_SHAPES, ids=lambda s: "N%d-B%d-T%d-a%d-%s" % s[:5])
+def test_forward_and_backward_match_oracle(shape):
+    from gpu_helpers import canaries_intact, run_backward, run_forward
+    N, B, T, a_dim, act, pad = shape
+    A, Wa, Wo, r0, J0, J1, alpha, act = random_case(N, B, T, a_dim, act, seed=N + B + T, pad_cols=pad)
+    active = [0, 1] if pad else None
+    ref_hist = orc.ring_forward_lean(A.double(), Wa.double(), J0, J1, Wo.double(), r0.double(), alpha, act)
+    g = torch.Generator().manual_seed(99)
+    cot = torch.randn(T, B, N, generator=g)
+    ref = orc.ring_backward_manual(cot.double(), A.double(), Wa.double(), J0, J1, Wo.double(), ref_hist,
+                                   r0.double(), alpha, act)
+    dA, dWa_, dWo_, dr0, dcot = _dev(A, Wa, Wo, r0, cot)
+    for prec in _modes_for(N, B, T, a_dim, 2 if pad else a_dim):
+        tol = TOL[prec]
+        f = run_forward(dA, dWa_, dWo_, dr0, J0, J1, alpha, act, prec, active, history=True, decode=False)
+        assert all(canaries_intact(b) for b in f["backs"]), "forward wrote outside its outputs"
+        assert torch.isfinite(f["hist"]).all()
+        assert orc.rel_err(f["hist"], ref_hist) < tol, prec
+        assert orc.rel_err(f["final"], ref_hist[-1]) < tol
+        b = run_backward(dA, dWa_, dWo_, dr0, J0, J1, alpha, act, f, grad_output=dcot, prec=prec, active=active)
+        assert all(canaries_intact(x) for x in b["backs"]), "backward wrote outside its outputs"
+        assert orc.rel_err(b["dWo"], ref["dWo"]) < tol, prec
+        assert orc.rel_err(b["dWa"], ref["dWa"]) < tol, prec
+        assert orc.rel_err(b["dr_init"], ref["dr_init"]) < tol, prec
+        assert abs(float(b["dJ"][0]) - float(ref["dJ0"])) < 10 * tol * max(1.0, abs(float(ref["dJ0"])))
+        assert abs(float(b["dJ"][1]) - float(ref["dJ1"])) < 10 * tol * max(1.0, abs(float(ref["dJ1"])))
+        if pad:
+            assert float(b["dWa"][2:].abs().max()) == 0.0  # skipped columns: exactly zero
+        # same call again: bit-identical (no atomics anywhere)
+        f2 = run_forward(dA, dWa_, dWo_, dr0, J0, J1, alpha, act, prec, active, history=True, decode=False)
+        b2 = run_backward(dA, dWa_, dWo_, dr0, J0, J1, alpha, act, f2, grad_output=dcot, prec=prec, active=active)
+        assert torch.equal(f["hist"], f2["hist"])
+        assert torch.equal(b["dWo"], b2["dWo"]) and torch.equal(b["dWa"], b2["dWa"])
+
+
+def _gold(name):
+    z = np.load(os.path.join(GOLD, name + ".npz"))
+    return {k: (torch.from_numpy(z[k]) if z[k].ndim else z[k].item()) for k in z.files}
+
+
+@pytest.mark.parametrize("name", ["ref_tanh_n24", "ref_relu_n40", "ref_gelu_n32_a4", "ref_gelu_n120"])
+def test_against_reference_golden_vectors(name):
+    """The committed outputs of the unmodified reference model: history and BPTT gradients."""
+    from gpu_helpers import run_backward, run_forward
+    g = _gold(name)
+    A, Wa, Wo, r0 = _dev(g["A"], g["Wa"], g["Wo"], g["r_init"])
+    cot = g["cot"].permute(1, 0, 2).contiguous().cuda()
+    f = run_forward(A, Wa, Wo, r0, g["J0"], g["J1"], g["alpha"], g["act"], "fp32")
+    assert orc.rel_err(f["hist"].permute(1, 0, 2), g["bump"]) < TOL["fp32"]
+    b = run_backward(A, Wa, Wo, r0, g["J0"], g["J1"], g["alpha"], g["act"], f, grad_output=cot)
+    assert orc.rel_err(b["dWo"], g["dWo_cot"]) < TOL["fp32"]
+    assert orc.rel_err(b["dWa"], g["dWa_cot"]) < TOL["fp32"]
+
+
+@pytest.mark.parametrize("name", ["ref_tanh_n24", "ref_gelu_n120"])
+def test_autograd_surface_against_reference_training_gradients(name):
+    """ring_rnn_cuda_func under the reference's own decode + losses reproduces the reference's loss and
+    parameter gradients (tests/golden: total.backward() of the unmodified model)."""
+    import cpp.ring_rnn_cuda as m
+    g = _gold(name)
+    A, r0, angle = _dev(g["A"], g["r_init"], g["angle"])
+    Wa = g["Wa"].cuda().requires_grad_(True)
+    Wo = g["Wo"].cuda().requires_grad_(True)
+    m.set_precision("fp32")
+    try:
+        hist = m.ring_rnn_cuda_func(A, Wa, g["J0"], g["J1"], Wo, r0, g["alpha"], g["act"])
+    finally:
+        m.set_precision("auto")
+    bump = hist.permute(1, 0, 2)
+    N = bump.shape[-1]
+    W7 = orc.w_delta7(N).cuda()
+    rd = bump @ W7
+    wave = rd / rd.max(dim=2, keepdim=True)[0]
+    phi = orc.preferred_angles(N).cuda()
+    th = torch.atan2((wave * torch.sin(phi)).sum(-1), (wave * torch.cos(phi)).sum(-1))
+    l_cos = torch.mean((torch.cos(th) - torch.cos(angle)) ** 2 + (torch.sin(th) - torch.sin(angle)) ** 2)
+    ta = bump.abs().sum(2)
+    l_amp = torch.mean((ta - ta[:, 0:1]) ** 2)
+    total = l_cos + 0.2 * l_amp
+    total.backward()
+    assert abs(float(total) - float(g["loss"])) < 1e-4 * max(1.0, abs(float(g["loss"])))
+    assert orc.rel_err(Wo.grad, g["dWo"]) < 2e-4
+    assert orc.rel_err(Wa.grad, g["dWa"]) < 2e-4
+
+
+FUSED_CASES = [(120, 128, 120, "tanh"), (24, 5, 12, "gelu"), (256, 64, 40, "relu")]
+
+
+@pytest.mark.parametrize("cfg", FUSED_CASES, ids=lambda c: "N%d-B%d-T%d-%s" % c)
+def test_fused_loss_step_matches_oracle(cfg):
+    """decode scalars, loss, closed-form loss gradient and the full fused fwd+bwd against the oracle's
+    reference-shaped training step (first case = the CPU-runnable benchmark configuration)."""
+    from gpu_helpers import angle_loss, run_backward, run_forward
+    N, B, T, act = cfg
+    case = orc.make_case(N, B, T, act, seed=0)
+    ref_loss, ref_dWo, ref_dWa, ref_hist = orc.train_step_ref(case, lean=True)
+    _, rx, ry, rta, _ = orc.fused_loss_terms(ref_hist.double(), case.target.double())
+    A, Wa, Wo, r0, tgt = _dev(case.A, case.Wa, case.Wo, case.r_init, case.target)
+    for prec in _modes_for(N, B, T, 2, 2):
+        tol = TOL[prec]
+        f = run_forward(A, Wa, Wo, r0, case.J0, case.J1, case.alpha, act, prec, history=False, decode=True)
+        assert orc.rel_err(f["x"], rx) < tol and orc.rel_err(f["y"], ry) < tol and orc.rel_err(f["ta"], rta) < tol
+        coefs, decoded, parts = angle_loss(f["x"], f["y"], f["ta"], tgt, 0.2, 1.0 / (B * T))
+        loss = float(parts[0] + 0.2 * parts[1])
+        assert abs(loss - float(ref_loss)) < tol * max(1.0, abs(float(ref_loss))), prec
+        ref_dec = orc.decode_angle(ref_hist)
+        assert float(orc.angular_error(decoded.cpu(), ref_dec).mean()) < 10 * tol
+        b = run_backward(A, Wa, Wo, r0, case.J0, case.J1, case.alpha, act, f, coefs=coefs, prec=prec)
+        assert orc.rel_err(b["dWo"], ref_dWo) < tol, prec
+        assert orc.rel_err(b["dWa"], ref_dWa) < tol, prec
+
+
+def test_fused_python_surface_and_rollout():
+    from rnn_train_ring_attractor_b200.fused import ring_rnn_fused, ring_rnn_rollout
+    case = orc.make_case(64, 32, 30, "tanh", seed=5)
+    ref_loss, ref_dWo, ref_dWa, ref_hist = orc.train_step_ref(case, lean=True)
+    A, r0, tgt = _dev(case.A, case.r_init, case.target)
+    Wa = case.Wa.cuda().requires_grad_(True)
+    Wo = case.Wo.cuda().requires_grad_(True)
+    loss, parts, decoded, final = ring_rnn_fused(A, Wa, case.J0, case.J1, Wo, r0, case.alpha, "tanh", tgt,
+                                                 precision="fp32")
+    loss.backward()
+    assert abs(float(loss) - float(ref_loss)) < 1e-4
+    assert orc.rel_err(Wo.grad, ref_dWo) < 1e-4 and orc.rel_err(Wa.grad, ref_dWa) < 1e-4
+    assert orc.rel_err(final, ref_hist[-1]) < 1e-4
+    dec2, final2 = ring_rnn_rollout(A, Wa.detach(), case.J0, case.J1, Wo.detach(), r0, case.alpha, "tanh",
+                                    precision="fp32")
+    assert float(orc.angular_error(dec2.cpu(), decoded.cpu()).max()) < 1e-4
+    assert torch.allclose(final2, final)
+
+
+def test_reference_style_model_trains_on_the_operator():
+    """A model written the way the reference's GeneralizedRingAttractorNoGain.forward is
+    (train_general_ring_no_gain.py:78-118): star-import, float J0/J1, alpha=0.15, zero-padded 16 action
+    columns, permute + W_delta7 + max-normalise, Adam + clip.  The loss trajectory must follow the same
+    model driven by the oracle recurrence on CPU."""
+    ns = {}
+    exec("from cpp.ring_rnn_cuda import *", ns)
+    assert "torch" in ns and "ring_rnn_cuda_func" in ns
+    ring = ns["ring_rnn_cuda_func"]
+    N, B, T, a_dim = 64, 32, 25, 16
+    torch.manual_seed(0)
+    Wo0 = torch.randn(N, N) / math.sqrt(N)
+    Wa0 = torch.randn(a_dim, N, N) / math.sqrt(N)
+    av, angle = orc.generate_av(B, T)
+    A = orc.av_to_action_signal(av, 1.0, a_dim)
+    r0 = orc.initial_bump_gaussian(angle[:, 0], N)
+    W7 = orc.w_delta7(N)
+
+    def run(device, fwd):
+        Wo = Wo0.clone().to(device).requires_grad_(True)
+        Wa = Wa0.clone().to(device).requires_grad_(True)
+        opt = torch.optim.Adam([Wo, Wa], lr=1e-3)
+        losses = []
+        for _ in range(5):
+            hist = fwd(A.to(device), Wa, -0.1, 0.1, Wo, r0.to(device), 0.15, "gelu")
+            bump = hist.permute(1, 0, 2)
+            rd = bump @ W7.to(device)
+            wave = rd / rd.max(dim=2, keepdim=True)[0]
+            phi = orc.preferred_angles(N).to(device)
+            th = torch.atan2((wave * torch.sin(phi)).sum(-1), (wave * torch.cos(phi)).sum(-1))
+            tgt = angle.to(device)
+            loss = torch.mean((torch.cos(th) - torch.cos(tgt)) ** 2 + (torch.sin(th) - torch.sin(tgt)) ** 2)
+            ta = bump.abs().sum(2)
+            total = loss + 0.2 * torch.mean((ta - ta[:, 0:1]) ** 2)
+            opt.zero_grad()
+            total.backward()
+            torch.nn.utils.clip_grad_norm_([Wo, Wa], 1.0)
+            opt.step()
+            losses.append(float(total))
+        return losses
+
+    got = run("cuda", ring)
+    want = run("cpu", orc.ring_forward_ref)
+    for a, b in zip(got, want):
+        assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (got, want)
+
+
+def test_raw_extension_objects():
+    """fwd_cuda.fwd / bwd_cuda.bwd with the reference's keyword names (cpp/fwd.cpp:49-55, cpp/bwd.cpp:101-123)."""
+    from cpp.rnn_cuda import bwd_cuda, fwd_cuda
+    A, Wa, Wo, r0, J0, J1, alpha, act = random_case(48, 16, 10, 16, "relu", seed=4, pad_cols=True)
+    ref_hist = orc.ring_forward_lean(A, Wa, J0, J1, Wo, r0, alpha, act)
+    cot = torch.randn(10, 16, 48)
+    ref = orc.ring_backward_manual(cot, A, Wa, J0, J1, Wo, ref_hist, r0, alpha, act)
+    dA, dWa, dWo, dr0, dcot = _dev(A, Wa, Wo, r0, cot)
+    hist = torch.empty(10, 16, 48, device="cuda")
+    fwd_cuda.fwd(A=dA, Wa=dWa, J0=J0, J1=J1, Wo=dWo, r_init=dr0, bump_history=hist, alpha=alpha, activation_type=0)
+    assert orc.rel_err(hist, ref_hist) < 1e-4
+    gWa = torch.zeros_like(dWa)
+    gWo = torch.zeros_like(dWo)
+    dummy = torch.empty(1, device="cuda")
+    bwd_cuda.bwd(grad_output=dcot, A=dA, Wa=dWa, J0=J0, J1=J1, Wo=dWo, bump_history=hist, re_history=dummy,
+                 r_init=dr0, grad_Wa=gWa, grad_Wo=gWo, alpha=alpha, activation_type=0, grad_r=dummy,
+                 W_eff_temp=dummy, grad_re_temp=dummy, grad_W_eff_temp_bf16=dummy, A_t_temp_bf16=dummy,
+                 grad_re_temp_T=dummy, cublas_handle=0)
+    assert orc.rel_err(gWo, ref["dWo"]) < 1e-4 and orc.rel_err(gWa, ref["dWa"]) < 1e-4
+    with pytest.raises(RuntimeError, match="contiguous"):
+        fwd_cuda.fwd(A=dA.transpose(0, 1), Wa=dWa, J0=J0, J1=J1, Wo=dWo, r_init=dr0, bump_history=hist,
+                     alpha=alpha, activation_type=0)
+
+
+def test_linearity_in_batch_at_scale():
+    """Size-independent property: weight gradients are additive over disjoint batch shards (what the
+    data-parallel split relies on), checked at a size the oracle could not hold (N=256, B=512, T=64)."""
+    from gpu_helpers import run_backward, run_forward
+    A, Wa, Wo, r0, J0, J1, alpha, act = random_case(256, 512, 64, 2, "gelu", seed=8)
+    cot = torch.randn(64, 512, 256)
+    dA, dWa, dWo, dr0, dcot = _dev(A, Wa, Wo, r0, cot)
+    full_f = run_forward(dA, dWa, dWo, dr0, J0, J1, alpha, act)
+    full = run_backward(dA, dWa, dWo, dr0, J0, J1, alpha, act, full_f, grad_output=dcot)
+    acc_o = torch.zeros_like(full["dWo"])
+    acc_a = torch.zeros_like(full["dWa"])
+    for lo in (0, 256):
+        sA, sr0 = dA[lo:lo + 256].contiguous(), dr0[lo:lo + 256].contiguous()
+        scot = dcot[:, lo:lo + 256].contiguous()
+        f = run_forward(sA, dWa, dWo, sr0, J0, J1, alpha, act)
+        assert torch.equal(f["hist"], full_f["hist"][:, lo:lo + 256])  # samples never interact
+        b = run_backward(sA, dWa, dWo, sr0, J0, J1, alpha, act, f, grad_output=scot)
+        acc_o += b["dWo"]
+        acc_a += b["dWa"]
+    assert orc.rel_err(acc_o, full["dWo"]) < 1e-5 and orc.rel_err(acc_a, full["dWa"]) < 1e-5
