@@ -66,6 +66,8 @@ SYMBOLS = {
     "ringrnn_timing_enable": (C.c_int, [C.c_int]),
     "ringrnn_timing_read": (C.c_int, [C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
     "ringrnn_timing_reset": (C.c_int, []),
+    "ringrnn_selftest_gemm": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                        C.c_longlong, C.c_int, C.c_void_p, C.c_void_p]),
 }
 
 _lib = None

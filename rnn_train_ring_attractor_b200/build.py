@@ -52,7 +52,7 @@ def build(force=False, verbose=False):
             sys.stderr.write(out)
         if pr.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}")
-    cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-lcuda"]
+    cmd = [nvcc, "-shared", "-o", LIB] + objs
     subprocess.run(cmd, check=True)
     return LIB
 

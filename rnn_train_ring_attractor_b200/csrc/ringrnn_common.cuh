@@ -90,6 +90,10 @@ size_t fp32_bwd_workspace_bytes(const RingRnnProblem& p);
 int fp32_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s);
 int fp32_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s);
 
+// split-K bf16 tensor-core GEMM (tc_gemm.cu); see there for the argument contract
+int tc_gemm(int mn_major, const void* A, const void* B, float* partial, float* out, int M, int N, long long K,
+            int nsplit, int* status, cudaStream_t s);
+
 // bf16 tensor-core path ----------------------------------------------------------------------
 bool bf16_supported(const RingRnnProblem& p);
 size_t bf16_fwd_workspace_bytes(const RingRnnProblem& p);
