@@ -1,0 +1,194 @@
+// bf16 mode of the ring-attractor operator: host orchestration of the tensor-core kernels
+// (tc_fwd.cu, tc_bwd.cu, tc_gemm.cu), operand preparation and buffer layouts.
+//
+// Layouts (NP = N rounded up to 128/256/512, BP = B rounded up to 128, C = NP/128):
+//   weights, forward  Wf [C*2*208, NP] bf16: block (q,s) rows = {Wo[i,:], Wl[i,:], Wr[i,:] for the 64 neurons i of
+//                     sub-slice s of CTA q, a row of ones, zero rows}; columns j >= N zero
+//   weights, backward Wb, same shape: rows = {Wo[:,j], Wl[:,j], Wr[:,j] for the 64 neurons j, ones, zeros}
+//   saved             Rh [T+1][BP][NP] bf16 (Rh[0] = r_init, Rh[t+1] = r_t) | Dh [T][BP][NP] bf16 = F'(re_t)
+//   backward scratch  DL [T*BP][3*NP] bf16 = [delta | L*delta | R*delta] (A operand of the weight-gradient
+//                     GEMM) | split-K partials | dWcat [3*NP][NP] fp32
+#include <string.h>
+
+#include "tc_recurrent.cuh"
+
+namespace ringrnn {
+
+using namespace tcr;
+
+struct TcFwdParams;
+struct TcBwdParams;
+int tc_forward_launch(int act, int NP, const CUtensorMap& tmW, const CUtensorMap& tmR0, const void* params,
+                      cudaStream_t s);
+
+namespace {
+
+int padded_n(int N) { return N <= 128 ? 128 : (N <= 256 ? 256 : (N <= 512 ? 512 : 0)); }
+int padded_b(int B) { return (B + 127) / 128 * 128; }
+int n_active_of(const RingRnnProblem& p) { return p.n_active < 0 ? p.a_dim : p.n_active; }
+
+// Wf / Wb blocks, see the header comment.  grid (NP/64 column chunks, C*2 blocks), block 256
+__global__ void prep_weights_kernel(const float* __restrict__ Wo, const float* __restrict__ Wl,
+                                    const float* __restrict__ Wr, int N, int NP, __nv_bfloat16* __restrict__ Wf,
+                                    __nv_bfloat16* __restrict__ Wb) {
+  const int blk = blockIdx.y;  // q*2 + s
+  const int n_first = blk * 64;
+  for (int idx = threadIdx.x; idx < RB * 64; idx += blockDim.x) {
+    const int rr = idx / 64, k = blockIdx.x * 64 + idx % 64;
+    float vf = 0.f, vb = 0.f;
+    if (rr < 192) {
+      const int m = rr / 64, n = n_first + rr % 64;
+      const float* W = (m == 0) ? Wo : (m == 1) ? Wl : Wr;
+      if (W != nullptr && n < N && k < N) {
+        vf = W[(size_t)n * N + k];
+        vb = W[(size_t)k * N + n];
+      }
+    } else if (rr == SUM_COL) {
+      vf = vb = (k < N) ? 1.f : 0.f;
+    }
+    const size_t at = ((size_t)blk * RB + rr) * NP + k;
+    Wf[at] = __float2bfloat16(vf);
+    if (Wb != nullptr) Wb[at] = __float2bfloat16(vb);
+  }
+}
+
+// R0[b][n] = bf16(r_init[b][n]) with zero padding
+__global__ void prep_r0_kernel(const float* __restrict__ r_init, int B, int N, int BP, int NP,
+                               __nv_bfloat16* __restrict__ R0) {
+  const size_t total = (size_t)BP * NP;
+  for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int b = (int)(idx / NP), n = (int)(idx % NP);
+    R0[idx] = __float2bfloat16((b < B && n < N) ? r_init[(size_t)b * N + n] : 0.f);
+  }
+}
+
+// dec_{x,y,ta}[b*T + t] = sum over slots of part[slot][k][t][b]
+__global__ void dec_reduce_kernel(const float* __restrict__ part, int slots, int B, int T, int BP, float* dec_x,
+                                  float* dec_y, float* dec_ta) {
+  const size_t total = (size_t)B * T;
+  for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / B), b = (int)(idx % B);
+    float acc[3] = {0.f, 0.f, 0.f};
+    for (int sl = 0; sl < slots; ++sl)
+#pragma unroll
+      for (int k = 0; k < 3; ++k) acc[k] += part[(((size_t)sl * 3 + k) * T + t) * BP + b];
+    const size_t o = (size_t)b * T + t;
+    if (dec_x) dec_x[o] = acc[0];
+    if (dec_y) dec_y[o] = acc[1];
+    if (dec_ta) dec_ta[o] = acc[2];
+  }
+}
+
+struct Layout {
+  int NP, BP, C;
+  size_t w_bytes, r0_bytes, dec_bytes, state_bytes;
+};
+
+Layout layout_of(const RingRnnProblem& p) {
+  Layout l;
+  l.NP = padded_n(p.N);
+  l.BP = padded_b(p.B);
+  l.C = l.NP / 128;
+  l.w_bytes = align_up((size_t)l.C * 2 * RB * l.NP * 2, 1024);
+  l.r0_bytes = align_up((size_t)l.BP * l.NP * 2, 1024);
+  l.dec_bytes = align_up((size_t)2 * l.C * 3 * p.T * l.BP * 4, 1024);
+  l.state_bytes = align_up((size_t)l.BP * l.NP * 2, 1024);  // one time slot of Rh / Dh
+  return l;
+}
+
+}  // namespace
+
+bool bf16_supported(const RingRnnProblem& p) {
+  return padded_n(p.N) != 0 && n_active_of(p) <= 2 && p.B >= 1 && p.T >= 1;
+}
+
+// FWD workspace: status(1024) | Wf | R0 | dec partials
+size_t bf16_fwd_workspace_bytes(const RingRnnProblem& p) {
+  const Layout l = layout_of(p);
+  return 1024 + l.w_bytes + l.r0_bytes + l.dec_bytes;
+}
+// SAVED: Rh[T+1] | Dh[T]
+size_t bf16_saved_bytes(const RingRnnProblem& p) {
+  const Layout l = layout_of(p);
+  return (size_t)(2 * p.T + 1) * l.state_bytes;
+}
+
+struct TcFwdParamsHost {
+  int B, T, N, BP, a_dim, colL, colR, n_tiles;
+  float J0, J1, alpha;
+  const float* A;
+  const float* r_init;
+  __nv_bfloat16* Rh;
+  __nv_bfloat16* Dh;
+  float* hist;
+  float* dec_part;
+  const float* dec_u;
+  const float* dec_v;
+  float* final_state;
+  int* status;
+};
+
+int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) {
+  const RingRnnProblem& p = a.p;
+  const Layout l = layout_of(p);
+  if (a.workspace == nullptr || a.workspace_bytes < bf16_fwd_workspace_bytes(p)) return RINGRNN_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(a.workspace) & 255) != 0) return RINGRNN_ERR_WORKSPACE;
+  const bool train = a.saved != nullptr;
+  if (train && (a.saved_bytes < bf16_saved_bytes(p) || (reinterpret_cast<uintptr_t>(a.saved) & 255) != 0))
+    return RINGRNN_ERR_WORKSPACE;
+  char* w = static_cast<char*>(a.workspace);
+  int* status = a.status != nullptr ? a.status : reinterpret_cast<int*>(w);
+  __nv_bfloat16* Wf = reinterpret_cast<__nv_bfloat16*>(w + 1024);
+  __nv_bfloat16* R0 = reinterpret_cast<__nv_bfloat16*>(w + 1024 + l.w_bytes);
+  float* dec_part = reinterpret_cast<float*>(w + 1024 + l.w_bytes + l.r0_bytes);
+  __nv_bfloat16* Rh = train ? static_cast<__nv_bfloat16*>(a.saved) : nullptr;
+  __nv_bfloat16* Dh = train ? Rh + (size_t)(p.T + 1) * l.BP * l.NP : nullptr;
+  if (train) R0 = Rh;  // slot 0 of the saved state doubles as the initial A operand
+
+  if (a.status == nullptr) RINGRNN_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), s));
+  const float* Wl = dp.n_mat > 1 ? dp.Wa + (size_t)dp.cols[0] * p.N * p.N : nullptr;
+  const float* Wr = dp.n_mat > 2 ? dp.Wa + (size_t)dp.cols[1] * p.N * p.N : nullptr;
+  {
+    LaunchScope ls(K_PREP, s);
+    prep_weights_kernel<<<dim3(l.NP / 64, l.C * 2), 256, 0, s>>>(p.Wo, Wl, Wr, p.N, l.NP, Wf, nullptr);
+  }
+  RINGRNN_CUDA_TRY(cudaGetLastError());
+  {
+    LaunchScope ls(K_PREP, s);
+    prep_r0_kernel<<<296, 256, 0, s>>>(p.r_init, p.B, p.N, l.BP, l.NP, R0);
+  }
+  RINGRNN_CUDA_TRY(cudaGetLastError());
+
+  CUtensorMap tmW, tmR0;
+  if (!make_tmap_bf16_2d(&tmW, Wf, (uint64_t)l.C * 2 * RB, (uint64_t)l.NP, RB, 64)) return RINGRNN_ERR_CUDA;
+  if (!make_tmap_bf16_2d(&tmR0, R0, (uint64_t)l.BP, (uint64_t)l.NP, 128, 64)) return RINGRNN_ERR_CUDA;
+
+  const bool want_dec = a.dec_x || a.dec_y || a.dec_ta;
+  TcFwdParamsHost fp;
+  memset(&fp, 0, sizeof(fp));
+  fp.B = p.B; fp.T = p.T; fp.N = p.N; fp.BP = l.BP; fp.a_dim = p.a_dim;
+  fp.colL = dp.n_mat > 1 ? dp.cols[0] : -1;
+  fp.colR = dp.n_mat > 2 ? dp.cols[1] : -1;
+  fp.n_tiles = l.BP / 128;
+  fp.J0 = p.J0; fp.J1 = p.J1; fp.alpha = p.alpha;
+  fp.A = p.A; fp.r_init = p.r_init;
+  fp.Rh = Rh; fp.Dh = Dh;
+  fp.hist = a.bump_history;
+  fp.dec_part = want_dec ? dec_part : nullptr;
+  fp.dec_u = a.dec_u; fp.dec_v = a.dec_v;
+  fp.final_state = a.final_state;
+  fp.status = status;
+  int rc = tc_forward_launch(p.activation, l.NP, tmW, tmR0, &fp, s);
+  if (rc != RINGRNN_OK) return rc;
+  if (want_dec) {
+    LaunchScope ls(K_LOSS, s);
+    dec_reduce_kernel<<<296, 256, 0, s>>>(dec_part, 2 * l.C, p.B, p.T, l.BP, a.dec_x, a.dec_y, a.dec_ta);
+    RINGRNN_CUDA_TRY(cudaGetLastError());
+  }
+  return RINGRNN_OK;
+}
+
+size_t bf16_bwd_workspace_bytes(const RingRnnProblem&) { return 0; }
+int bf16_backward(const RingRnnBwdArgs&, const DevProblem&, cudaStream_t) { return RINGRNN_ERR_UNSUPPORTED; }
+
+}  // namespace ringrnn

@@ -30,10 +30,10 @@ def random_case(N, B, T, a_dim, act, seed, alpha=0.1, scale=None, pad_cols=False
     scale = scale if scale is not None else 1.0 / math.sqrt(N)
     Wo = torch.randn(N, N, generator=g) * scale
     Wa = torch.randn(a_dim, N, N, generator=g) * scale
-    A = torch.rand(B, T, a_dim, generator=g) * 0.3
+    A = torch.rand(B, T, a_dim, generator=g)
     if pad_cols:
         A[:, :, 2:] = 0.0
-    r0 = torch.rand(B, N, generator=g)
+    r0 = torch.rand(B, N, generator=g) - 0.5  # zero mean keeps J0*sum(r) small, so the activations are not saturated
     return A, Wa, Wo, r0, -0.1, 0.1, alpha, act
 
 
