@@ -20,6 +20,8 @@ struct TcFwdParams;
 struct TcBwdParams;
 int tc_forward_launch(int act, int NP, const CUtensorMap& tmW, const CUtensorMap& tmR0, const void* params,
                       cudaStream_t s);
+int tc_backward_launch(int NP, const CUtensorMap& tmW, const void* params, cudaStream_t s);
+__global__ void grad_j_kernel(const float* __restrict__ raw, const float* __restrict__ Wo, size_t NN, float* grad_J);
 
 namespace {
 
@@ -47,7 +49,7 @@ __global__ void prep_weights_kernel(const float* __restrict__ Wo, const float* _
       vf = vb = (k < N) ? 1.f : 0.f;
     }
     const size_t at = ((size_t)blk * RB + rr) * NP + k;
-    Wf[at] = __float2bfloat16(vf);
+    if (Wf != nullptr) Wf[at] = __float2bfloat16(vf);
     if (Wb != nullptr) Wb[at] = __float2bfloat16(vb);
   }
 }
@@ -188,7 +190,142 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   return RINGRNN_OK;
 }
 
-size_t bf16_bwd_workspace_bytes(const RingRnnProblem&) { return 0; }
-int bf16_backward(const RingRnnBwdArgs&, const DevProblem&, cudaStream_t) { return RINGRNN_ERR_UNSUPPORTED; }
+// ---- backward ------------------------------------------------------------------------------------------
+
+namespace {
+
+// dWcat [3*NP][NP] -> grad_Wo = J1 * block 0, grad_Wa[colL] = block 1, grad_Wa[colR] = block 2 (unpadded);
+// raw = block 0 unscaled and unpadded (for the J0 / J1 gradients)
+__global__ void unpack_dw_kernel(const float* __restrict__ dWcat, int N, int NP, float J1, int colL, int colR,
+                                 float* grad_Wo, float* grad_Wa, float* raw) {
+  const size_t NN = (size_t)N * N;
+  for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < NN; e += (size_t)gridDim.x * blockDim.x) {
+    const int i = (int)(e / N), j = (int)(e % N);
+    const float g0 = dWcat[(size_t)i * NP + j];
+    grad_Wo[e] = J1 * g0;
+    raw[e] = g0;
+    if (colL >= 0) grad_Wa[(size_t)colL * NN + e] = dWcat[((size_t)NP + i) * NP + j];
+    if (colR >= 0) grad_Wa[(size_t)colR * NN + e] = dWcat[((size_t)2 * NP + i) * NP + j];
+  }
+}
+
+int gemm_splits(const Layout& l, int T) {
+  const int m_tiles = 3 * l.NP / 128;
+  int ns = 148 / m_tiles;
+  const long long K = (long long)T * l.BP;
+  while (ns > 1 && K / ns < 256) --ns;
+  return ns < 1 ? 1 : ns;
+}
+
+struct BwdLayout {
+  size_t w_bytes, dl_bytes, partial_bytes, dw_bytes, raw_bytes;
+  int nsplit;
+};
+
+BwdLayout bwd_layout_of(const RingRnnProblem& p, const Layout& l) {
+  BwdLayout b;
+  b.nsplit = gemm_splits(l, p.T);
+  b.w_bytes = l.w_bytes;
+  b.dl_bytes = align_up((size_t)p.T * l.BP * 3 * l.NP * 2, 1024);
+  b.partial_bytes = align_up((size_t)b.nsplit * 3 * l.NP * l.NP * 4, 1024);
+  b.dw_bytes = align_up((size_t)3 * l.NP * l.NP * 4, 1024);
+  b.raw_bytes = align_up((size_t)p.N * p.N * 4, 1024);
+  return b;
+}
+
+}  // namespace
+
+// BWD workspace: status(1024) | Wb | DL | split-K partials | dWcat | raw
+size_t bf16_bwd_workspace_bytes(const RingRnnProblem& p) {
+  const Layout l = layout_of(p);
+  const BwdLayout b = bwd_layout_of(p, l);
+  return 1024 + b.w_bytes + b.dl_bytes + b.partial_bytes + b.dw_bytes + b.raw_bytes;
+}
+
+struct TcBwdParamsHost {
+  int B, T, N, BP, a_dim, colL, colR, n_tiles;
+  float J0, J1, alpha;
+  const float* A;
+  const __nv_bfloat16* Rh;
+  const __nv_bfloat16* Dh;
+  const float* grad_output;
+  const float* coef_x;
+  const float* coef_y;
+  const float* coef_s;
+  const float* dec_u;
+  const float* dec_v;
+  __nv_bfloat16* DL;
+  float* grad_r_init;
+  int* status;
+};
+
+int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s) {
+  const RingRnnProblem& p = a.p;
+  const Layout l = layout_of(p);
+  const BwdLayout bl = bwd_layout_of(p, l);
+  if (a.workspace == nullptr || a.workspace_bytes < bf16_bwd_workspace_bytes(p)) return RINGRNN_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(a.workspace) & 255) != 0) return RINGRNN_ERR_WORKSPACE;
+  if (a.saved == nullptr || a.saved_bytes < bf16_saved_bytes(p) || (reinterpret_cast<uintptr_t>(a.saved) & 255) != 0)
+    return RINGRNN_ERR_WORKSPACE;
+  char* w = static_cast<char*>(a.workspace);
+  int* status = a.status != nullptr ? a.status : reinterpret_cast<int*>(w);
+  w += 1024;
+  __nv_bfloat16* Wb = reinterpret_cast<__nv_bfloat16*>(w);
+  w += bl.w_bytes;
+  __nv_bfloat16* DL = reinterpret_cast<__nv_bfloat16*>(w);
+  w += bl.dl_bytes;
+  float* partial = reinterpret_cast<float*>(w);
+  w += bl.partial_bytes;
+  float* dWcat = reinterpret_cast<float*>(w);
+  w += bl.dw_bytes;
+  float* raw = reinterpret_cast<float*>(w);
+  const __nv_bfloat16* Rh = static_cast<const __nv_bfloat16*>(a.saved);
+  const __nv_bfloat16* Dh = Rh + (size_t)(p.T + 1) * l.BP * l.NP;
+
+  if (a.status == nullptr) RINGRNN_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), s));
+  const float* Wl = dp.n_mat > 1 ? dp.Wa + (size_t)dp.cols[0] * p.N * p.N : nullptr;
+  const float* Wr = dp.n_mat > 2 ? dp.Wa + (size_t)dp.cols[1] * p.N * p.N : nullptr;
+  const int colL = dp.n_mat > 1 ? dp.cols[0] : -1, colR = dp.n_mat > 2 ? dp.cols[1] : -1;
+  {
+    LaunchScope ls(K_PREP, s);
+    prep_weights_kernel<<<dim3(l.NP / 64, l.C * 2), 256, 0, s>>>(p.Wo, Wl, Wr, p.N, l.NP, nullptr, Wb);
+  }
+  RINGRNN_CUDA_TRY(cudaGetLastError());
+  CUtensorMap tmW;
+  if (!make_tmap_bf16_2d(&tmW, Wb, (uint64_t)l.C * 2 * RB, (uint64_t)l.NP, RB, 64)) return RINGRNN_ERR_CUDA;
+
+  TcBwdParamsHost bp;
+  memset(&bp, 0, sizeof(bp));
+  bp.B = p.B; bp.T = p.T; bp.N = p.N; bp.BP = l.BP; bp.a_dim = p.a_dim;
+  bp.colL = colL; bp.colR = colR;
+  bp.n_tiles = l.BP / 128;
+  bp.J0 = p.J0; bp.J1 = p.J1; bp.alpha = p.alpha;
+  bp.A = p.A; bp.Rh = Rh; bp.Dh = Dh;
+  bp.grad_output = a.grad_output;
+  bp.coef_x = a.coef_x; bp.coef_y = a.coef_y; bp.coef_s = a.coef_s;
+  bp.dec_u = a.dec_u; bp.dec_v = a.dec_v;
+  bp.DL = DL;
+  bp.grad_r_init = a.grad_r_init;
+  bp.status = status;
+  int rc = tc_backward_launch(l.NP, tmW, &bp, s);
+  if (rc != RINGRNN_OK) return rc;
+
+  // dWcat[3NP, NP] = DL^T [3NP, T*BP] x Rh[0..T) [T*BP, NP]
+  rc = tc_gemm(1, DL, Rh, partial, dWcat, 3 * l.NP, l.NP, (long long)p.T * l.BP, bl.nsplit, status, s);
+  if (rc != RINGRNN_OK) return rc;
+  const size_t NN = (size_t)p.N * p.N;
+  RINGRNN_CUDA_TRY(cudaMemsetAsync(a.grad_Wa, 0, sizeof(float) * (size_t)p.a_dim * NN, s));
+  {
+    LaunchScope ls(K_REDUCE, s);
+    unpack_dw_kernel<<<296, 256, 0, s>>>(dWcat, p.N, l.NP, p.J1, colL, colR, a.grad_Wo, a.grad_Wa, raw);
+  }
+  RINGRNN_CUDA_TRY(cudaGetLastError());
+  if (a.grad_J != nullptr) {
+    LaunchScope ls(K_REDUCE, s);
+    grad_j_kernel<<<1, 1024, 0, s>>>(raw, p.Wo, NN, a.grad_J);
+    RINGRNN_CUDA_TRY(cudaGetLastError());
+  }
+  return RINGRNN_OK;
+}
 
 }  // namespace ringrnn
