@@ -279,8 +279,14 @@ def main():
     ap.add_argument("--precision", default="auto", choices=["auto", "bf16", "fp32"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--seq-len", type=int, default=0, help="override T (profiling on a smaller case of the same kernels)")
+    ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling)")
     args = ap.parse_args()
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.seq_len:
+        wl["T"] = args.seq_len
+    if args.batch:
+        wl["B"] = args.batch
     if args.impl == "reference":
         run_reference(args, wl)
     else:
