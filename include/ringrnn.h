@@ -28,7 +28,8 @@ enum {
   RINGRNN_ERR_WORKSPACE = 3,   /* workspace / saved buffer missing, misaligned or too small    */
   RINGRNN_ERR_CUDA = 4,        /* a CUDA runtime call failed (see ringrnn_last_cuda_error)     */
   RINGRNN_ERR_UNSUPPORTED = 5, /* valid request that this precision mode cannot serve          */
-  RINGRNN_ERR_DEVICE = 6       /* a kernel reported a bounded wait that ran out                */
+  RINGRNN_ERR_DEVICE = 6,      /* a kernel reported a bounded wait that ran out                */
+  RINGRNN_ERR_TOO_LARGE = 7    /* size exceeds the capacity of the library's built-in scratch  */
 };
 
 /* activation codes: the enum order of cpp/cuda_common.cuh:56 and the activation_map of
@@ -162,6 +163,27 @@ int ringrnn_bwd_cuda(const void* grad_output, const void* A, const void* Wa, flo
 int ringrnn_angle_loss(int B, int T, const float* dec_x, const float* dec_y, const float* dec_ta,
                        const float* target, float bump_weight, float inv_count, float* coef_x, float* coef_y,
                        float* coef_s, float* decoded, float* loss_out, float* scratch, void* stream);
+
+/* ringrnn_angle_loss without the caller-supplied scratch.  No counterpart in the reference.
+ *
+ * Same computation, arguments and outputs as ringrnn_angle_loss, minus `scratch`: the per-sample partial
+ * losses go to an array that lives inside the library (2 * RINGRNN_STATIC_LOSS_MAX_B floats = 512 KB of
+ * device memory, held by every GPU that loads the library until the process exits).  It is meant for hosts
+ * that may not allocate device memory at the point where they need the loss: a serving process whose
+ * memory is owned entirely by its framework's pool, so that a raw allocation would fail or fragment it, or a
+ * latency-critical loop that cannot afford the device-wide synchronisation an allocation implies.  The call
+ * itself performs no cudaMalloc / cudaFree and calls no allocating library routine.
+ *   - B > RINGRNN_STATIC_LOSS_MAX_B is rejected with RINGRNN_ERR_TOO_LARGE before anything is launched.
+ *   - The first call on each device looks up the array's device address (once per device, with that device
+ *     current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array, and it keeps the previous call's contents.  Nothing in it has
+ *     to start at zero: each call overwrites entries [0,B) and [B,2B) before it reads them and reads no
+ *     others.  Two calls that overlap in time on the same GPU (different streams or threads) race on it;
+ *     order them on one stream or with events. */
+#define RINGRNN_STATIC_LOSS_MAX_B 65536
+int ringrnn_angle_loss_static(int B, int T, const float* dec_x, const float* dec_y, const float* dec_ta,
+                              const float* target, float bump_weight, float inv_count, float* coef_x,
+                              float* coef_y, float* coef_s, float* decoded, float* loss_out, void* stream);
 
 /* Launch accounting and per-kernel timing (the reference's counterpart is the NVTX / cudaProfiler
  * bracketing in legacy/bwd_fp32.py:705-740 and utils/benchmark.py:58-79).

@@ -14,6 +14,8 @@ ACT = {"relu": 0, "gelu": 1, "tanh": 2, "silu": 3}  # cpp/ring_rnn_cuda.py:63
 PREC = {"fp32": 0, "bf16": 1}
 WS_FWD, WS_SAVED, WS_BWD = 0, 1, 2
 ERR_UNSUPPORTED = 5
+ERR_TOO_LARGE = 7
+STATIC_LOSS_MAX_B = 65536
 
 c_float_p = C.c_void_p
 
@@ -60,6 +62,9 @@ SYMBOLS = {
     "ringrnn_angle_loss": (C.c_int, [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float,
                                      C.c_float, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                      C.c_void_p, C.c_void_p]),
+    "ringrnn_angle_loss_static": (C.c_int, [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                            C.c_float, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                            C.c_void_p, C.c_void_p]),
     "ringrnn_launch_count": (C.c_longlong, []),
     "ringrnn_timing_slots": (C.c_int, []),
     "ringrnn_timing_name": (C.c_char_p, [C.c_int]),

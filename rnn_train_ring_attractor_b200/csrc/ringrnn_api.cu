@@ -98,6 +98,7 @@ extern "C" const char* ringrnn_strerror(int status) {
     case RINGRNN_ERR_CUDA: return "CUDA runtime error";
     case RINGRNN_ERR_UNSUPPORTED: return "request not supported by this precision mode";
     case RINGRNN_ERR_DEVICE: return "a bounded device-side wait ran out";
+    case RINGRNN_ERR_TOO_LARGE: return "size exceeds the capacity of the library's built-in scratch array";
     default: return "unknown status";
   }
 }

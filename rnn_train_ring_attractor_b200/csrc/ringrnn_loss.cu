@@ -7,6 +7,8 @@
 // amplitude loss: (ta_t - ta_0)^2 (train/train_ring_attractor.py:289-296).  The kernel also emits the
 // coefficients of the closed-form gradient with respect to r_t:
 //   dL/dr_t = coef_x*u + coef_y*v + coef_s*sign(r_t).
+#include <mutex>
+
 #include "ringrnn_common.cuh"
 
 namespace ringrnn {
@@ -105,6 +107,62 @@ extern "C" int ringrnn_angle_loss(int B, int T, const float* dec_x, const float*
   }
   RINGRNN_CUDA_TRY(cudaGetLastError());
   { LaunchScope ls(K_LOSS, s); loss_finish_kernel<<<1, LT, 0, s>>>(B, scratch, inv_count, loss_out); }
+  RINGRNN_CUDA_TRY(cudaGetLastError());
+  return RINGRNN_OK;
+}
+
+// ---- the same loss with library-owned scratch -------------------------------------------------------------
+// For callers that cannot allocate device memory where they need the loss (a process whose framework pool owns
+// all of it, or a loop that cannot take the device-wide synchronisation of an allocation).  The per-sample
+// partial sums live in this file-scope array; every GPU that loads the library carries its 512 KB.
+static __device__ __align__(256) float g_static_loss_scratch[2 * RINGRNN_STATIC_LOSS_MAX_B];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+float* g_static_addr[kMaxDevices];  // device address of g_static_loss_scratch on each device, looked up once
+
+// In host code the array's name is only a handle for the runtime, not a device pointer: the address a kernel
+// may use has to be asked for, on the device that will run the kernel.
+int static_scratch_address(float** out) {
+  int dev = -1;
+  RINGRNN_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return RINGRNN_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (g_static_addr[dev] == nullptr) {
+    float* ptr = nullptr;
+    RINGRNN_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_loss_scratch));
+    if (ptr == nullptr) return RINGRNN_ERR_CUDA;
+    g_static_addr[dev] = ptr;
+  }
+  *out = g_static_addr[dev];
+  return RINGRNN_OK;
+}
+}  // namespace
+
+extern "C" int ringrnn_angle_loss_static(int B, int T, const float* dec_x, const float* dec_y, const float* dec_ta,
+                                         const float* target, float bump_weight, float inv_count, float* coef_x,
+                                         float* coef_y, float* coef_s, float* decoded, float* loss_out,
+                                         void* stream) {
+  using namespace ringrnn;
+  if (B <= 0 || T <= 0) return RINGRNN_ERR_SHAPE;
+  if (B > RINGRNN_STATIC_LOSS_MAX_B) return RINGRNN_ERR_TOO_LARGE;
+  if (!dec_x || !dec_y || !dec_ta || !target || !coef_x || !coef_y || !coef_s || !loss_out) return RINGRNN_ERR_ARG;
+  float* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);  // first call per device: the lookup; later calls: a table read
+  if (rc != RINGRNN_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // entries [0,B) and [B,2B) are written by the first kernel before the second reads them: nothing to clear
+  {
+    LaunchScope ls(K_LOSS, s);
+    angle_loss_kernel<<<B, LT, 0, s>>>(B, T, dec_x, dec_y, dec_ta, target, bump_weight, inv_count, coef_x, coef_y,
+                                       coef_s, decoded, scratch);
+  }
+  RINGRNN_CUDA_TRY(cudaGetLastError());
+  {
+    LaunchScope ls(K_LOSS, s);
+    loss_finish_kernel<<<1, LT, 0, s>>>(B, scratch, inv_count, loss_out);
+  }
   RINGRNN_CUDA_TRY(cudaGetLastError());
   return RINGRNN_OK;
 }

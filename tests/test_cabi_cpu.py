@@ -35,7 +35,7 @@ def test_header_symbols_all_exported(L):
 def test_version_and_strerror(L):
     assert L.ringrnn_version() >= 100
     assert L.ringrnn_strerror(0) == b"ok"
-    for code in range(1, 7):
+    for code in range(1, 8):
         assert len(L.ringrnn_strerror(code)) > 3
     assert L.ringrnn_strerror(99) == b"unknown status"
 
