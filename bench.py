@@ -36,6 +36,12 @@ WORKLOADS = {
     "c3": dict(N=512, B=4096, T=512, act="gelu", max_av=0.1 * math.pi, cpu_slice=(64, 16)),
     "c4": dict(N=1024, B=8192, T=2000, act="tanh", max_av=0.05 * math.pi, cpu_slice=(16, 8)),
 }
+# DRAM bytes (read + write) per sample-timestep of each bf16-mode kernel at N=512, from the ncu captures summarised
+# under profiles/ (taken at T=64, B=4096; traffic is proportional to B*T).  None = no capture for that kernel/mode.
+NCU_DRAM_BYTES_PER_SAMPLE_STEP = {
+    ("bf16", 512): {"fwd_recurrent": (16.67e6 + 516.53e6) / (4096 * 64), "bwd_recurrent": (551.35e6 + 761.25e6) / (4096 * 64),
+                    "dw_product": (1074.6e6 + 3.94e6) / (4096 * 64)},
+}
 METRIC = "fwd+bwd sample-timesteps/s"
 UNIT = "sample-timesteps/s"
 
@@ -241,8 +247,10 @@ def run_ours(args, wl):
         ms_launch = cand[dom][0] / cand[dom][1]
         achieved = flops_per_launch / (ms_launch * 1e-3) / 1e12
         peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
+        per_unit = NCU_DRAM_BYTES_PER_SAMPLE_STEP.get((prec, N), {}).get(dom)
+        traffic = per_unit * B_local * T if per_unit is not None else None
         roof = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": None, "peak_source": f"{peak_src} (sustained bf16 GEMM)",
+                "frac": achieved / peak, "traffic": traffic, "peak_source": f"{peak_src} (sustained bf16 GEMM)",
                 "ms_per_launch": ms_launch,
                 "kernels_ms_per_step": {k: v[0] / args.steps for k, v in kern.items() if v[1] > 0}}
 
