@@ -70,8 +70,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const TcBwdParams p) {
     for (int i = 0; i < 8; ++i) mbar_init(bars + OFF_A_FULL + 8 * i, 1);
     mbar_init(bars + OFF_D_FULL, 1);
     mbar_init(bars + OFF_D_FULL + 8, 1);
-    mbar_init(bars + OFF_D_EMPTY, 8);
-    mbar_init(bars + OFF_D_EMPTY + 8, 4);
+    mbar_init(bars + OFF_D_EMPTY, 8);  // all eight epilogue warps drain each accumulator
+    mbar_init(bars + OFF_D_EMPTY + 8, 8);
     mbar_init(bars + OFF_MMA_DONE, 1);
     mbar_init(bars + OFF_ALL_FREE, C);
     fence_mbar_init();
@@ -165,13 +165,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const TcBwdParams p) {
     }
   } else {
     reg_inc<232>();
-    // ---------------- epilogue: warps 4-7 own sub-slice 0, warps 8-11 sub-slice 1; thread = sample ----------------
-    const int s = (warp - 4) >> 2, quarter = warp & 3;
+    // ---------------- epilogue: thread = sample.  Warps 4-7 (h = 0) own columns [0,32) and warps 8-11 (h = 1)
+    // columns [32,64) of both 64-neuron sub-slices; master[s*32 + j] is neuron 128q + 64s + 32h + j. ----------------
+    const int h = (warp - 4) >> 2, quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const int n0 = (int)q * 128 + s * 64;
-    const int kc_own = 2 * (int)q + s;
-    const uint32_t tile_addr = a_base + kc_own * CHUNK_BYTES;
+    const int nq = (int)q * 128 + 32 * h;
     const float J0 = p.J0, J1 = p.J1, alpha = p.alpha, beta = 1.f - p.alpha;
     const bool has_coef = p.coef_x != nullptr;
     uint32_t g = 0;
@@ -181,138 +180,169 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const TcBwdParams p) {
       float master[64];  // carry on entry of `produce`, g_t afterwards
 #pragma unroll
       for (int j = 0; j < 64; ++j) master[j] = 0.f;
-      float L = 0.f, R = 0.f;
+      float L = 0.f, R = 0.f;        // action scalars of the step whose delta is in flight
+      float Ln = 0.f, Rn = 0.f, cx = 0.f, cy = 0.f, cs = 0.f;  // prefetched for the next `produce`
+      uint4 dv[8], rv[8];            // prefetched rows of F'(re_t) and r_t (bf16): [s*4 + v]
 
-      // delta_t from the carry: adds dL/dr_t, applies alpha*F'(re_t), publishes the bf16 chunk, writes DL
-      auto produce = [&](int t) {
-        L = 0.f;
-        R = 0.f;
-        float cx = 0.f, cy = 0.f, cs = 0.f;
+      // loads for produce(t); issued before the wait on the accumulators so that their latency is hidden
+      auto prefetch = [&](int t) {
+        Ln = 0.f; Rn = 0.f; cx = 0.f; cy = 0.f; cs = 0.f;
         if (valid) {
           const float* at = p.A + ((size_t)b * T + t) * p.a_dim;
-          if (p.colL >= 0) L = __ldg(at + p.colL);
-          if (p.colR >= 0) R = __ldg(at + p.colR);
+          if (p.colL >= 0) Ln = __ldg(at + p.colL);
+          if (p.colR >= 0) Rn = __ldg(at + p.colR);
           if (has_coef) {
             cx = __ldg(p.coef_x + (size_t)b * T + t);
             cy = __ldg(p.coef_y + (size_t)b * T + t);
             cs = __ldg(p.coef_s + (size_t)b * T + t);
           }
         }
-        const uint4* dsrc = reinterpret_cast<const uint4*>(p.Dh + ((size_t)t * p.BP + b) * NP + n0);
-        const uint4* rsrc = reinterpret_cast<const uint4*>(p.Rh + ((size_t)(t + 1) * p.BP + b) * NP + n0);
-        uint4 dv[8], rv[8];
 #pragma unroll
-        for (int v = 0; v < 8; ++v) dv[v] = __ldg(dsrc + v);
+        for (int s = 0; s < 2; ++s) {
+          const uint4* dsrc = reinterpret_cast<const uint4*>(p.Dh + ((size_t)t * p.BP + b) * NP + nq + 64 * s);
+          const uint4* rsrc = reinterpret_cast<const uint4*>(p.Rh + ((size_t)(t + 1) * p.BP + b) * NP + nq + 64 * s);
 #pragma unroll
-        for (int v = 0; v < 8; ++v) rv[v] = has_coef ? __ldg(rsrc + v) : make_uint4(0u, 0u, 0u, 0u);
-        if (t > 0) {  // warm L2 for the next step's rows
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(p.Dh + ((size_t)(t - 1) * p.BP + b) * NP + n0));
-          if (has_coef) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.Rh + ((size_t)t * p.BP + b) * NP + n0));
-        }
-        if (p.grad_output != nullptr && valid) {
-          const float* gsrc = p.grad_output + ((size_t)t * p.B + b) * p.N + n0;
-          if ((p.N & 3) == 0) {
-#pragma unroll
-            for (int j = 0; j < 64; j += 4)
-              if (n0 + j < p.N) {
-                const float4 gv = __ldg(reinterpret_cast<const float4*>(gsrc + j));
-                master[j] += gv.x; master[j + 1] += gv.y; master[j + 2] += gv.z; master[j + 3] += gv.w;
-              }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 64; ++j)
-              if (n0 + j < p.N) master[j] += __ldg(gsrc + j);
+          for (int v = 0; v < 4; ++v) {
+            dv[s * 4 + v] = __ldg(dsrc + v);
+            rv[s * 4 + v] = has_coef ? __ldg(rsrc + v) : make_uint4(0u, 0u, 0u, 0u);
           }
-        }
-        uint32_t packed[32];
-        __nv_bfloat16* drow = p.DL + ((size_t)t * p.BP + b) * (3 * NP) + n0;
-#pragma unroll
-        for (int v = 0; v < 8; ++v) {
-          const uint32_t dw[4] = {dv[v].x, dv[v].y, dv[v].z, dv[v].w};
-          const uint32_t rw[4] = {rv[v].x, rv[v].y, rv[v].z, rv[v].w};
-          uint32_t o0[4], o1[4], o2[4];
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            float dl[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int idx = v * 8 + h * 2 + e;
-              float gg = master[idx];
-              if (has_coef) {
-                const float rr = e ? bf16_hi(rw[h]) : bf16_lo(rw[h]);
-                const float sg = (rr > 0.f) ? 1.f : ((rr < 0.f) ? -1.f : 0.f);
-                gg = fmaf(cx, uv[s * 64 + idx], gg);
-                gg = fmaf(cy, uv[128 + s * 64 + idx], gg);
-                gg = fmaf(cs, sg, gg);
-              }
-              master[idx] = gg;
-              const float dact = e ? bf16_hi(dw[h]) : bf16_lo(dw[h]);
-              dl[e] = alpha * dact * gg;
-            }
-            o0[h] = pack_bf16x2(dl[0], dl[1]);
-            o1[h] = pack_bf16x2(L * dl[0], L * dl[1]);
-            o2[h] = pack_bf16x2(R * dl[0], R * dl[1]);
-            packed[v * 4 + h] = o0[h];
-          }
-          *reinterpret_cast<uint4*>(drow + v * 8) = make_uint4(o0[0], o0[1], o0[2], o0[3]);
-          *reinterpret_cast<uint4*>(drow + NP + v * 8) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
-          *reinterpret_cast<uint4*>(drow + 2 * NP + v * 8) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
-        }
-#pragma unroll
-        for (int v = 0; v < 8; ++v) {
-          const uint32_t addr = tile_addr + row * 128 + (((uint32_t)v ^ ((uint32_t)row & 7u)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * v]),
-                       "r"(packed[4 * v + 1]), "r"(packed[4 * v + 2]), "r"(packed[4 * v + 3])
-                       : "memory");
-        }
-        fence_proxy_async_smem();
-        named_bar_sync(1 + s, 128);
-        if (quarter == 0 && lane == 0) {
-          mbar_arrive(bars + OFF_A_FULL + 8 * kc_own);
-          for (uint32_t r = 0; r < (uint32_t)C; ++r)
-            if (r != q) dsmem_bulk_copy(tile_addr, tile_addr, CHUNK_BYTES, bars + OFF_A_FULL + 8 * kc_own, r);
         }
       };
 
-      produce(T - 1);
-      for (int t = T - 1; t >= 0; --t, ++g) {
-        mbar_wait(bars + OFF_D_FULL + 8 * s, g & 1u, wctx, 307);
-        tcgen05_fence_after();
-        uint32_t sraw;
-        tmem_ld1(tmem_base + lane_base + SUM_COL, &sraw);  // sum_i delta_t[b,i], from D_0
-        tmem_ld_wait();
-        const float c0 = J0 * __uint_as_float(sraw);
+      // delta_t from the carry: adds dL/dr_t, applies alpha*F'(re_t), publishes the bf16 chunks, writes DL
+      auto produce = [&](int t) {
+        L = Ln;
+        R = Rn;
+        if (p.grad_output != nullptr && valid) {
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          uint32_t zo[32], zl[32], zr[32];
-          const uint32_t col = tmem_base + lane_base + s * 256 + cc * 32;
-          tmem_ld32(col, zo);
-          tmem_ld32(col + 64, zl);
-          tmem_ld32(col + 128, zr);
-          tmem_ld_wait();
+          for (int s = 0; s < 2; ++s) {
+            const float* gsrc = p.grad_output + ((size_t)t * p.B + b) * p.N + nq + 64 * s;
+            if ((p.N & 3) == 0) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int idx = cc * 32 + j;
-            float c = fmaf(beta, master[idx], c0);
-            c = fmaf(J1, __uint_as_float(zo[j]), c);
-            c = fmaf(L, __uint_as_float(zl[j]), c);
-            c = fmaf(R, __uint_as_float(zr[j]), c);
-            master[idx] = (n0 + idx < p.N) ? c : 0.f;
+              for (int j = 0; j < 32; j += 4)
+                if (nq + 64 * s + j < p.N) {
+                  const float4 gv = __ldg(reinterpret_cast<const float4*>(gsrc + j));
+                  master[s * 32 + j] += gv.x; master[s * 32 + j + 1] += gv.y;
+                  master[s * 32 + j + 2] += gv.z; master[s * 32 + j + 3] += gv.w;
+                }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nq + 64 * s + j < p.N) master[s * 32 + j] += __ldg(gsrc + j);
+            }
           }
         }
-        tcgen05_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(bars + OFF_D_EMPTY + 8 * s);
-          if (s == 1) mbar_arrive(bars + OFF_D_EMPTY);
+        uint32_t packed[32];
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          __nv_bfloat16* drow = p.DL + ((size_t)t * p.BP + b) * (3 * NP) + nq + 64 * s;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint32_t dw[4] = {dv[s * 4 + v].x, dv[s * 4 + v].y, dv[s * 4 + v].z, dv[s * 4 + v].w};
+            const uint32_t rw[4] = {rv[s * 4 + v].x, rv[s * 4 + v].y, rv[s * 4 + v].z, rv[s * 4 + v].w};
+            uint32_t o0[4], o1[4], o2[4];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              float dl[2];
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int j = v * 8 + w * 2 + e;
+                const int idx = s * 32 + j;
+                float gg = master[idx];
+                if (has_coef) {
+                  const float rr = e ? bf16_hi(rw[w]) : bf16_lo(rw[w]);
+                  const float sg = (rr > 0.f) ? 1.f : ((rr < 0.f) ? -1.f : 0.f);
+                  gg = fmaf(cx, uv[64 * s + 32 * h + j], gg);
+                  gg = fmaf(cy, uv[128 + 64 * s + 32 * h + j], gg);
+                  gg = fmaf(cs, sg, gg);
+                }
+                master[idx] = gg;
+                const float dact = e ? bf16_hi(dw[w]) : bf16_lo(dw[w]);
+                dl[e] = alpha * dact * gg;
+              }
+              o0[w] = pack_bf16x2(dl[0], dl[1]);
+              o1[w] = pack_bf16x2(L * dl[0], L * dl[1]);
+              o2[w] = pack_bf16x2(R * dl[0], R * dl[1]);
+              packed[s * 16 + v * 4 + w] = o0[w];
+            }
+            *reinterpret_cast<uint4*>(drow + v * 8) = make_uint4(o0[0], o0[1], o0[2], o0[3]);
+            *reinterpret_cast<uint4*>(drow + NP + v * 8) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+            *reinterpret_cast<uint4*>(drow + 2 * NP + v * 8) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+          }
+        }
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          const uint32_t tile_addr = a_base + (2 * (int)q + s) * CHUNK_BYTES;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint32_t unit = (uint32_t)(4 * h + v);
+            const uint32_t addr = tile_addr + row * 128 + ((unit ^ ((uint32_t)row & 7u)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[s * 16 + 4 * v]),
+                         "r"(packed[s * 16 + 4 * v + 1]), "r"(packed[s * 16 + 4 * v + 2]),
+                         "r"(packed[s * 16 + 4 * v + 3])
+                         : "memory");
+          }
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(1, 256);
+        if (warp == 4 && lane == 0) {
+#pragma unroll
+          for (int s = 0; s < 2; ++s) {
+            const int kc = 2 * (int)q + s;
+            const uint32_t tile_addr = a_base + kc * CHUNK_BYTES;
+            mbar_arrive(bars + OFF_A_FULL + 8 * kc);
+            for (uint32_t r = 0; r < (uint32_t)C; ++r)
+              if (r != q) dsmem_bulk_copy(tile_addr, tile_addr, CHUNK_BYTES, bars + OFF_A_FULL + 8 * kc, r);
+          }
+        }
+      };
+
+      prefetch(T - 1);
+      produce(T - 1);
+      for (int t = T - 1; t >= 0; --t, ++g) {
+        if (t > 0) prefetch(t - 1);
+        float c0 = 0.f;
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          mbar_wait(bars + OFF_D_FULL + 8 * s, g & 1u, wctx, 307);
+          tcgen05_fence_after();
+          if (s == 0) {
+            uint32_t sraw;
+            tmem_ld1(tmem_base + lane_base + SUM_COL, &sraw);  // sum_i delta_t[b,i]
+            tmem_ld_wait();
+            c0 = J0 * __uint_as_float(sraw);
+          }
+#pragma unroll
+          for (int c16 = 0; c16 < 2; ++c16) {
+            uint32_t zo[16], zl[16], zr[16];
+            const uint32_t col = tmem_base + lane_base + s * 256 + 32 * h + 16 * c16;
+            tmem_ld16(col, zo);
+            tmem_ld16(col + 64, zl);
+            tmem_ld16(col + 128, zr);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int idx = s * 32 + c16 * 16 + j;
+              float c = fmaf(beta, master[idx], c0);
+              c = fmaf(J1, __uint_as_float(zo[j]), c);
+              c = fmaf(L, __uint_as_float(zl[j]), c);
+              c = fmaf(R, __uint_as_float(zr[j]), c);
+              master[idx] = (nq + 64 * s + c16 * 16 + j < p.N) ? c : 0.f;
+            }
+          }
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bars + OFF_D_EMPTY + 8 * s);
         }
         mbar_wait<true>(bars + OFF_ALL_FREE, g & 1u, wctx, 308);
         if (t > 0) {
           produce(t - 1);
         } else if (p.grad_r_init != nullptr && valid) {
 #pragma unroll
-          for (int j = 0; j < 64; ++j)
-            if (n0 + j < p.N) p.grad_r_init[(size_t)b * p.N + n0 + j] = master[j];
+          for (int s = 0; s < 2; ++s)
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nq + 64 * s + j < p.N) p.grad_r_init[(size_t)b * p.N + nq + 64 * s + j] = master[s * 32 + j];
         }
       }
     }

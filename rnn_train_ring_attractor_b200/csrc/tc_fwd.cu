@@ -64,8 +64,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     for (int i = 0; i < 8; ++i) mbar_init(bars + OFF_A_FULL + 8 * i, 1);
     mbar_init(bars + OFF_D_FULL, 1);
     mbar_init(bars + OFF_D_FULL + 8, 1);
-    mbar_init(bars + OFF_D_EMPTY, 8);      // 4 warps that drain D_0 + 4 warps that read its row-sum column
-    mbar_init(bars + OFF_D_EMPTY + 8, 4);
+    mbar_init(bars + OFF_D_EMPTY, 8);      // all eight epilogue warps drain each accumulator
+    mbar_init(bars + OFF_D_EMPTY + 8, 8);
     mbar_init(bars + OFF_MMA_DONE, 1);
     mbar_init(bars + OFF_ALL_FREE, C);
     fence_mbar_init();
@@ -172,13 +172,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     }
   } else {
     reg_inc<232>();
-    // ---------------- epilogue: warps 4-7 own sub-slice 0, warps 8-11 sub-slice 1; thread = sample ----------------
-    const int s = (warp - 4) >> 2, quarter = warp & 3;
+    // ---------------- epilogue: thread = sample.  Warps 4-7 (h = 0) own columns [0,32) and warps 8-11 (h = 1)
+    // columns [32,64) of BOTH 64-neuron sub-slices, so every accumulator is drained by all eight warps at once
+    // (two warps per scheduler) and the part of the step that nothing overlaps -- the epilogue of the last
+    // sub-slice -- is 32 elements per thread.  master[s*32 + j] is neuron 128q + 64s + 32h + j. ----------------
+    const int h = (warp - 4) >> 2, quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const int n0 = (int)q * 128 + s * 64;  // first neuron of this thread's sub-slice
-    const int kc_own = 2 * (int)q + s;
-    const int slot = kc_own;
+    const int nq = (int)q * 128 + 32 * h;  // neuron of master[0]; sub-slice s adds 64*s
+    const int slot = 2 * (int)q + h;
     const float J0 = p.J0, J1 = p.J1, alpha = p.alpha, beta = 1.f - p.alpha;
     const bool want_dec = p.dec_part != nullptr;
     uint32_t g = 0;
@@ -187,7 +189,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       const bool valid = b < p.B;
       float master[64];
 #pragma unroll
-      for (int j = 0; j < 64; ++j) master[j] = (valid && n0 + j < p.N) ? __ldg(p.r_init + (size_t)b * p.N + n0 + j) : 0.f;
+      for (int s = 0; s < 2; ++s)
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int n = nq + 64 * s + j;
+          master[s * 32 + j] = (valid && n < p.N) ? __ldg(p.r_init + (size_t)b * p.N + n) : 0.f;
+        }
       for (int t = 0; t < T; ++t, ++g) {
         float L = 0.f, R = 0.f;
         if (valid) {
@@ -195,78 +202,124 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           if (p.colL >= 0) L = __ldg(at + p.colL);
           if (p.colR >= 0) R = __ldg(at + p.colR);
         }
-        mbar_wait(bars + OFF_D_FULL + 8 * s, g & 1u, wctx, 207);
-        tcgen05_fence_after();
-        uint32_t sraw;
-        tmem_ld1(tmem_base + lane_base + SUM_COL, &sraw);  // row sum of r_{t-1}, from D_0
-        tmem_ld_wait();
-        const float c0 = J0 * __uint_as_float(sraw);
         uint32_t packed[32];
-        float px = 0.f, py = 0.f, pa = 0.f;
+        float px = 0.f, py = 0.f, pa = 0.f, c0 = 0.f;
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
+        for (int s = 0; s < 2; ++s) {
+          mbar_wait(bars + OFF_D_FULL + 8 * s, g & 1u, wctx, 207);
+          tcgen05_fence_after();
           uint32_t yo[32], yl[32], yr[32];
-          const uint32_t col = tmem_base + lane_base + s * 256 + cc * 32;
-          tmem_ld32(col, yo);
-          tmem_ld32(col + 64, yl);
-          tmem_ld32(col + 128, yr);
-          tmem_ld_wait();
+          const uint32_t col = tmem_base + lane_base + s * 256 + 32 * h;
+          if (s == 0) {
+            uint32_t sraw;
+            tmem_ld1(tmem_base + lane_base + SUM_COL, &sraw);  // row sum of r_{t-1}
+            tmem_ld32(col, yo);
+            tmem_ld32(col + 64, yl);
+            tmem_ld32(col + 128, yr);
+            tmem_ld_wait();
+            c0 = J0 * __uint_as_float(sraw);
+          } else {
+            tmem_ld32(col, yo);
+            tmem_ld32(col + 64, yl);
+            tmem_ld32(col + 128, yr);
+            tmem_ld_wait();
+          }
+          // the accumulator is in registers: hand it back to the MMA warp
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bars + OFF_D_EMPTY + 8 * s);
           uint32_t dpk[16];
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            float rn[2], dd[2];
+          for (int j0 = 0; j0 < 32; j0 += 8) {
+            float re[8], f[8], d[8];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int idx = cc * 32 + j + h;
-              float re = fmaf(J1, __uint_as_float(yo[j + h]), c0);
-              re = fmaf(L, __uint_as_float(yl[j + h]), re);
-              re = fmaf(R, __uint_as_float(yr[j + h]), re);
-              float f, d;
-              act_pair<ACT>(re, f, d);
-              float r = fmaf(alpha, f, beta * master[idx]);
-              if (n0 + idx >= p.N) { r = 0.f; d = 0.f; }
+            for (int e = 0; e < 8; ++e) {
+              float v = fmaf(J1, __uint_as_float(yo[j0 + e]), c0);
+              v = fmaf(L, __uint_as_float(yl[j0 + e]), v);
+              re[e] = fmaf(R, __uint_as_float(yr[j0 + e]), v);
+            }
+            act_group<ACT, 8>(re, f, d);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int idx = s * 32 + j0 + e;
+              float r = fmaf(alpha, f[e], beta * master[idx]);
+              if (nq + 64 * s + j0 + e >= p.N) { r = 0.f; d[e] = 0.f; }
               master[idx] = r;
-              rn[h] = r;
-              dd[h] = d;
+              f[e] = r;
               if (want_dec) {
-                px = fmaf(r, uv[s * 64 + idx], px);
-                py = fmaf(r, uv[128 + s * 64 + idx], py);
+                px = fmaf(r, uv[64 * s + 32 * h + j0 + e], px);
+                py = fmaf(r, uv[128 + 64 * s + 32 * h + j0 + e], py);
                 pa += fabsf(r);
               }
             }
-            packed[cc * 16 + (j >> 1)] = pack_bf16x2(rn[0], rn[1]);
-            dpk[j >> 1] = pack_bf16x2(dd[0], dd[1]);
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+              packed[s * 16 + ((j0 + e) >> 1)] = pack_bf16x2(f[e], f[e + 1]);
+              dpk[(j0 + e) >> 1] = pack_bf16x2(d[e], d[e + 1]);
+            }
           }
           if (p.Dh != nullptr) {
-            uint4* dst = reinterpret_cast<uint4*>(p.Dh + ((size_t)t * p.BP + b) * NP + n0 + cc * 32);
+            uint4* dst = reinterpret_cast<uint4*>(p.Dh + ((size_t)t * p.BP + b) * NP + nq + 64 * s);
 #pragma unroll
             for (int v = 0; v < 4; ++v) dst[v] = make_uint4(dpk[4 * v], dpk[4 * v + 1], dpk[4 * v + 2], dpk[4 * v + 3]);
           }
         }
-        // TMEM reads of this step are done: hand the accumulators back to the MMA warp
-        tcgen05_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(bars + OFF_D_EMPTY + 8 * s);
-          if (s == 1) mbar_arrive(bars + OFF_D_EMPTY);
-        }
-        if (p.Rh != nullptr) {
-          uint4* dst = reinterpret_cast<uint4*>(p.Rh + ((size_t)(t + 1) * p.BP + b) * NP + n0);
+        // every CTA of the cluster has finished reading r_{t-1} (waited for in every step so that no phase of
+        // the barrier is skipped); then publish r_t
+        mbar_wait<true>(bars + OFF_ALL_FREE, g & 1u, wctx, 208);
+        if (t + 1 < T) {
 #pragma unroll
-          for (int v = 0; v < 8; ++v)
-            dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+          for (int s = 0; s < 2; ++s) {
+            const uint32_t tile_addr = a_base + (2 * (int)q + s) * CHUNK_BYTES;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const uint32_t unit = (uint32_t)(4 * h + v);
+              const uint32_t addr = tile_addr + row * 128 + ((unit ^ ((uint32_t)row & 7u)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[s * 16 + 4 * v]),
+                           "r"(packed[s * 16 + 4 * v + 1]), "r"(packed[s * 16 + 4 * v + 2]),
+                           "r"(packed[s * 16 + 4 * v + 3])
+                           : "memory");
+            }
+          }
+          fence_proxy_async_smem();
+          named_bar_sync(1, 256);
+          if (warp == 4 && lane == 0) {
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+              const int kc = 2 * (int)q + s;
+              const uint32_t tile_addr = a_base + kc * CHUNK_BYTES;
+              mbar_arrive(bars + OFF_A_FULL + 8 * kc);
+              for (uint32_t r = 0; r < (uint32_t)C; ++r)
+                if (r != q) dsmem_bulk_copy(tile_addr, tile_addr, CHUNK_BYTES, bars + OFF_A_FULL + 8 * kc, r);
+            }
+          }
+        }
+        // off the critical path: saved state, fp32 history, decode sums
+        if (p.Rh != nullptr) {
+#pragma unroll
+          for (int s = 0; s < 2; ++s) {
+            uint4* dst = reinterpret_cast<uint4*>(p.Rh + ((size_t)(t + 1) * p.BP + b) * NP + nq + 64 * s);
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              dst[v] = make_uint4(packed[s * 16 + 4 * v], packed[s * 16 + 4 * v + 1], packed[s * 16 + 4 * v + 2],
+                                  packed[s * 16 + 4 * v + 3]);
+          }
         }
         if (p.hist != nullptr && valid) {
-          float* dst = p.hist + ((size_t)t * p.B + b) * p.N + n0;
-          if ((p.N & 3) == 0) {
 #pragma unroll
-            for (int j = 0; j < 64; j += 4)
-              if (n0 + j < p.N)
-                *reinterpret_cast<float4*>(dst + j) = make_float4(master[j], master[j + 1], master[j + 2], master[j + 3]);
-          } else {
+          for (int s = 0; s < 2; ++s) {
+            float* dst = p.hist + ((size_t)t * p.B + b) * p.N + nq + 64 * s;
+            if ((p.N & 3) == 0) {
 #pragma unroll
-            for (int j = 0; j < 64; ++j)
-              if (n0 + j < p.N) dst[j] = master[j];
+              for (int j = 0; j < 32; j += 4)
+                if (nq + 64 * s + j < p.N)
+                  *reinterpret_cast<float4*>(dst + j) = make_float4(master[s * 32 + j], master[s * 32 + j + 1],
+                                                                    master[s * 32 + j + 2], master[s * 32 + j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nq + 64 * s + j < p.N) dst[j] = master[s * 32 + j];
+            }
           }
         }
         if (want_dec) {
@@ -275,31 +328,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           dp[(size_t)T * p.BP] = py;
           dp[(size_t)2 * T * p.BP] = pa;
         }
-        // every CTA of the cluster has finished reading r_{t-1} (waited for in every step so that no phase of
-        // the barrier is skipped); then publish r_t
-        mbar_wait<true>(bars + OFF_ALL_FREE, g & 1u, wctx, 208);
-        if (t + 1 < T) {
-          const uint32_t tile_addr = a_base + kc_own * CHUNK_BYTES;
-#pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            const uint32_t addr = tile_addr + row * 128 + (((uint32_t)v ^ ((uint32_t)row & 7u)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * v]),
-                         "r"(packed[4 * v + 1]), "r"(packed[4 * v + 2]), "r"(packed[4 * v + 3])
-                         : "memory");
-          }
-          fence_proxy_async_smem();
-          named_bar_sync(1 + s, 128);
-          if (quarter == 0 && lane == 0) {
-            mbar_arrive(bars + OFF_A_FULL + 8 * kc_own);
-            for (uint32_t r = 0; r < (uint32_t)C; ++r)
-              if (r != q) dsmem_bulk_copy(tile_addr, tile_addr, CHUNK_BYTES, bars + OFF_A_FULL + 8 * kc_own, r);
-          }
-        }
       }
       if (p.final_state != nullptr && valid) {
 #pragma unroll
-        for (int j = 0; j < 64; ++j)
-          if (n0 + j < p.N) p.final_state[(size_t)b * p.N + n0 + j] = master[j];
+        for (int s = 0; s < 2; ++s)
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (nq + 64 * s + j < p.N) p.final_state[(size_t)b * p.N + nq + 64 * s + j] = master[s * 32 + j];
       }
     }
   }

@@ -27,7 +27,7 @@ namespace tcr {
 constexpr int RB = 208;              // rows of one weight block
 constexpr int WT_BYTES = RB * 128;   // one [RB x 64] bf16 tile
 constexpr int CHUNK_BYTES = 128 * 128;  // one [128 samples x 64 neurons] bf16 chunk
-constexpr int THREADS = 384;         // warps 0-3: TMA / MMA / relay / idle; warps 4-7, 8-11: epilogue
+constexpr int THREADS = 384;         // warps 0-3: TMA / MMA / relay / idle; warps 4-11: epilogue
 constexpr int SMEM_LIMIT = 232448;   // 227 KB
 constexpr int TMEM_COLS = 512;
 constexpr int SUM_COL = 192;
@@ -75,36 +75,58 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
-// F(x) and F'(x) together, cheap evaluations whose error is far below bf16 resolution.
-template <int ACT>
-__device__ __forceinline__ void act_pair(float x, float& f, float& d) {
+// F(x) and F'(x) for a group of G independent elements, written stage by stage over the group so that the
+// G dependency chains interleave (the epilogue runs with two warps per scheduler: without instruction-level
+// parallelism inside the thread it is latency-bound).  Evaluation error is far below bf16 resolution.
+template <int ACT, int G>
+__device__ __forceinline__ void act_group(const float* x, float* f, float* d) {
   if constexpr (ACT == RINGRNN_ACT_RELU) {
-    f = fmaxf(x, 0.f);
-    d = x > 0.f ? 1.f : 0.f;
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+      f[i] = fmaxf(x[i], 0.f);
+      d[i] = x[i] > 0.f ? 1.f : 0.f;
+    }
   } else if constexpr (ACT == RINGRNN_ACT_TANH) {
-    float y;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-    f = y;
-    d = fmaf(-y, y, 1.f);
+#pragma unroll
+    for (int i = 0; i < G; ++i) asm("tanh.approx.f32 %0, %1;" : "=f"(f[i]) : "f"(x[i]));
+#pragma unroll
+    for (int i = 0; i < G; ++i) d[i] = fmaf(-f[i], f[i], 1.f);
   } else if constexpr (ACT == RINGRNN_ACT_SILU) {
-    const float s = __frcp_rn(1.f + __expf(-x));
-    f = x * s;
-    d = s * fmaf(x, 1.f - s, 1.f);
+    float s[G];
+#pragma unroll
+    for (int i = 0; i < G; ++i) s[i] = __fdividef(1.f, 1.f + __expf(-x[i]));
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+      f[i] = x[i] * s[i];
+      d[i] = s[i] * fmaf(x[i], 1.f - s[i], 1.f);
+    }
   } else {
     // exact-erf GELU: Phi(x) = (1 + erf(x/sqrt2))/2 with erf from Abramowitz-Stegun 7.1.26 (|err| < 1.5e-7);
     // exp(-x^2/2) is shared with the density term of the derivative Phi(x) + x*phi(x).
-    const float z = fabsf(x) * 0.70710678118654752f;
-    const float t = __frcp_rn(fmaf(0.3275911f, z, 1.f));
-    float poly = fmaf(t, 1.061405429f, -1.453152027f);
-    poly = fmaf(t, poly, 1.421413741f);
-    poly = fmaf(t, poly, -0.284496736f);
-    poly = fmaf(t, poly, 0.254829592f);
-    poly *= t;
-    const float e = __expf(-z * z);
-    const float erf_abs = fmaf(-poly, e, 1.f);
-    const float cdf = 0.5f + 0.5f * copysignf(erf_abs, x);
-    f = x * cdf;
-    d = fmaf(x * 0.3989422804014327f, e, cdf);
+    float z[G], t[G], e[G], poly[G];
+#pragma unroll
+    for (int i = 0; i < G; ++i) z[i] = fabsf(x[i]) * 0.70710678118654752f;
+#pragma unroll
+    for (int i = 0; i < G; ++i) t[i] = __fdividef(1.f, fmaf(0.3275911f, z[i], 1.f));
+#pragma unroll
+    for (int i = 0; i < G; ++i) e[i] = exp2f(-1.4426950408889634f * z[i] * z[i]);
+#pragma unroll
+    for (int i = 0; i < G; ++i) poly[i] = fmaf(t[i], 1.061405429f, -1.453152027f);
+#pragma unroll
+    for (int i = 0; i < G; ++i) poly[i] = fmaf(t[i], poly[i], 1.421413741f);
+#pragma unroll
+    for (int i = 0; i < G; ++i) poly[i] = fmaf(t[i], poly[i], -0.284496736f);
+#pragma unroll
+    for (int i = 0; i < G; ++i) poly[i] = fmaf(t[i], poly[i], 0.254829592f);
+#pragma unroll
+    for (int i = 0; i < G; ++i) poly[i] *= t[i];
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+      const float erf_abs = fmaf(-poly[i], e[i], 1.f);
+      const float cdf = 0.5f + 0.5f * copysignf(erf_abs, x[i]);
+      f[i] = x[i] * cdf;
+      d[i] = fmaf(x[i] * 0.3989422804014327f, e[i], cdf);
+    }
   }
 }
 
