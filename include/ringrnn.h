@@ -202,7 +202,9 @@ int ringrnn_timing_reset(void);
 /* Library self-test: one split-K bf16 GEMM on the tcgen05 tensor-core path the bf16 mode is built from
  * (TMA-fed shared-memory ring, TMEM accumulator).  No counterpart in the reference; it exists so that the
  * operand layouts can be checked in isolation.  out[M,N] fp32 = A * B over K:
- *   mn_major = 1: A is [K,M] and B is [K,N] bf16 row-major;  mn_major = 0: A is [M,K] and B is [N,K].
+ *   mn_major = 1: A is [K,M] and B is [K,N] bf16 row-major;  mn_major = 0: A is [M,K] and B is [N,K];
+ *   mn_major = 2: as 0, computed by CTA pairs (cta_group::2 MMAs, M % 256 == 0, N % 128 == 0 or N % 224 == 0,
+ *   nsplit ignored).
  * M % 128 == 0, N % 128 == 0, partial holds nsplit*M*N floats, status is a zero-initialised device int. */
 int ringrnn_selftest_gemm(int mn_major, const void* A, const void* B, float* partial, float* out, int M, int N,
                           long long K, int nsplit, int* status, void* stream);

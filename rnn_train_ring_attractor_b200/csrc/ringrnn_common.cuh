@@ -94,6 +94,8 @@ int fp32_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
 int tc_gemm(int mn_major, const void* A, const void* B, float* partial, float* out, int M, int N, long long K,
             int nsplit, int* status, cudaStream_t s);
 
+int tc_gemm_pair(const void* A, const void* B, float* out, int M, int N, long long K, int* status, cudaStream_t s);
+
 // bf16 tensor-core path ----------------------------------------------------------------------
 bool bf16_supported(const RingRnnProblem& p);
 size_t bf16_fwd_workspace_bytes(const RingRnnProblem& p);

@@ -11,6 +11,8 @@
 // TMA into a ring of shared-memory stages, warp 1 issues tcgen05.mma into one TMEM accumulator, warps 2-5
 // move the finished accumulator to global memory as an fp32 partial; a second kernel sums the partials in a
 // fixed order (no atomics, bit-reproducible).
+#include <string.h>
+
 #include "ringrnn_common.cuh"
 #include "tc_ptx.cuh"
 
@@ -192,6 +194,154 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
+
+// ---- CTA-pair variant (K-major operands): a cluster of two CTAs owns a 256 x NT output tile; each CTA loads its
+// own 128 rows of A and half of the B rows, the even CTA issues cta_group::2 MMAs for both.  Used by the
+// library self-test to validate the pair building blocks the recurrent kernels rely on.
+template <int NT>
+struct PairCfg {
+  static constexpr int KC = 64;
+  static constexpr int A_BYTES = 128 * 128;
+  static constexpr int B_BYTES = (NT / 2) * 128;  // this CTA's half of the B rows
+  static constexpr int STAGE = A_BYTES + B_BYTES;
+  static constexpr int NSTAGE = (200 * 1024) / STAGE < 8 ? (200 * 1024) / STAGE : 8;
+  static constexpr int SMEM = NSTAGE * STAGE + 1024 + 256;
+  static constexpr int TMEM_COLS = NT <= 32 ? 32 : NT <= 64 ? 64 : NT <= 128 ? 128 : NT <= 256 ? 256 : 512;  // power of two
+};
+
+template <int NT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 float* __restrict__ out, int M_total, int N_total, long long K_total, int* status) {
+  using Cfg = PairCfg<NT>;
+  static_assert(NT <= 256, "one MMA instruction along N");
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + Cfg::NSTAGE * Cfg::STAGE;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (Cfg::NSTAGE + s); };
+  const uint32_t done_bar = bars + 8u * (2 * Cfg::NSTAGE);
+  const uint32_t tmem_slot = done_bar + 8;
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(gen + Cfg::NSTAGE * Cfg::STAGE + 8 * (2 * Cfg::NSTAGE + 1));
+  volatile int* dead = reinterpret_cast<volatile int*>(gen + Cfg::NSTAGE * Cfg::STAGE + 8 * (2 * Cfg::NSTAGE + 1) + 4);
+  const WaitCtx wctx{dead, status};
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t h = cluster_ctarank();  // 0 = even CTA (issues the MMAs), 1 = odd CTA
+  const int pair = blockIdx.x >> 1;
+  const int m0 = pair * 256 + (int)h * 128, n0 = blockIdx.y * NT;
+  const int iters = (int)((K_total + Cfg::KC - 1) / Cfg::KC);
+
+  if (threadIdx.x == 0) {
+    *dead = 0;
+    for (int s = 0; s < Cfg::NSTAGE; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(done_bar, 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS);
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot_p;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      for (int it = 0; it < iters; ++it) {
+        const int s = it % Cfg::NSTAGE;
+        const uint32_t round = it / Cfg::NSTAGE;
+        if (it >= Cfg::NSTAGE && !mbar_wait(empty_bar(s), (round - 1) & 1u, wctx, 111)) break;
+        const uint32_t a_dst = base + s * Cfg::STAGE, b_dst = a_dst + Cfg::A_BYTES;
+        if (h == 0) mbar_arrive_expect_tx(full_bar(s), 2 * Cfg::STAGE);  // both CTAs' bytes land on this barrier
+        const int k = it * Cfg::KC;
+        tma_load_2d_pair(a_dst, &tmA, full_bar(s), k, m0);
+        tma_load_2d_pair(b_dst, &tmB, full_bar(s), k, n0 + (int)h * (NT / 2));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && h == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(256, NT, 0, 0);
+      bool ok = true;
+      for (int it = 0; it < iters && ok; ++it) {
+        const int s = it % Cfg::NSTAGE;
+        const uint32_t round = it / Cfg::NSTAGE;
+        ok = mbar_wait(full_bar(s), round & 1u, wctx, 112);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t a_src = base + s * Cfg::STAGE, b_src = a_src + Cfg::A_BYTES;
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss_pair(tmem_base, make_smem_desc(a_src + ks * 32, 16, 1024), make_smem_desc(b_src + ks * 32, 16, 1024),
+                       idesc, (it > 0 || ks > 0) ? 1u : 0u);
+        umma_commit_pair(empty_bar(s), 3);
+      }
+      umma_commit_pair(done_bar, 3);
+    }
+  } else {
+    const int q = warp & 3;
+    const bool ok = mbar_wait(done_bar, 0, wctx, 113);
+    tcgen05_fence_after();
+    const int row = m0 + q * 32 + lane;
+    float* orow = out + (size_t)row * N_total + n0;
+    for (int c0 = 0; c0 < NT; c0 += 32) {
+      uint32_t v[32];
+      if (iters > 0 && ok) {
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0u;
+      }
+      if (row < M_total) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(orow + c0 + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                   __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+}
+
+template <int NT>
+int launch_gemm_pair(const void* A, const void* B, float* out, int M_total, int N_total, long long K_total, int* status,
+                     cudaStream_t s) {
+  using Cfg = PairCfg<NT>;
+  CUtensorMap tmA, tmB;
+  if (!make_tmap_bf16_2d(&tmA, A, (uint64_t)M_total, (uint64_t)K_total, 128, 64) ||
+      !make_tmap_bf16_2d(&tmB, B, (uint64_t)N_total, (uint64_t)K_total, NT / 2, 64))
+    return RINGRNN_ERR_CUDA;
+  RINGRNN_CUDA_TRY(cudaFuncSetAttribute(gemm_pair_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * (M_total / 256), N_total / NT, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  {
+    LaunchScope ls(K_DW, s);
+    RINGRNN_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<NT>, tmA, tmB, out, M_total, N_total, K_total, status));
+  }
+  return RINGRNN_OK;
+}
+
 // out[e] = scale * sum_s partial[s][e]   (fixed order)
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int nsplit, size_t elems, float* out) {
   for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < elems; e += (size_t)gridDim.x * blockDim.x) {
@@ -259,11 +409,21 @@ int tc_gemm(int mn_major, const void* A, const void* B, float* partial, float* o
   return RINGRNN_OK;
 }
 
+// CTA-pair K-major GEMM: out[M,N] = A[M,K] * B[N,K]^T, M % 256 == 0, N a multiple of 256, 224 or 128 (the pair MMA wants N % 32 == 0) (N % NT == 0)
+int tc_gemm_pair(const void* A, const void* B, float* out, int M, int N, long long K, int* status, cudaStream_t s) {
+  if (M % 256 != 0) return RINGRNN_ERR_SHAPE;
+  if (N % 256 == 0) return launch_gemm_pair<256>(A, B, out, M, N, K, status, s);
+  if (N % 224 == 0) return launch_gemm_pair<224>(A, B, out, M, N, K, status, s);
+  if (N % 128 == 0) return launch_gemm_pair<128>(A, B, out, M, N, K, status, s);
+  return RINGRNN_ERR_SHAPE;
+}
+
 }  // namespace ringrnn
 
 // Library self-test hook: one bf16 tensor-core GEMM with caller-provided device buffers.
 extern "C" int ringrnn_selftest_gemm(int mn_major, const void* A, const void* B, float* partial, float* out, int M,
                                      int N, long long K, int nsplit, int* status, void* stream) {
   if (!A || !B || !partial || !out) return RINGRNN_ERR_ARG;
+  if (mn_major == 2) return ringrnn::tc_gemm_pair(A, B, out, M, N, K, status, static_cast<cudaStream_t>(stream));
   return ringrnn::tc_gemm(mn_major, A, B, partial, out, M, N, K, nsplit, status, static_cast<cudaStream_t>(stream));
 }
