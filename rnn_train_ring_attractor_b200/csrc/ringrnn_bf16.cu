@@ -1,8 +1,8 @@
 // bf16 mode of the ring-attractor operator: host orchestration of the tensor-core kernels
 // (tc_fwd.cu, tc_bwd.cu, tc_gemm.cu), operand preparation and buffer layouts.
 //
-// Layouts (NP = N rounded up to 128/256/512, BP = B rounded up to 128, C = NP/128):
-//   weights, forward  Wf [C*2*208, NP] bf16: block (q,s) rows = {Wo[i,:], Wl[i,:], Wr[i,:] for the 64 neurons i of
+// Layouts (NP = N rounded up to 128/256/512, BP = B rounded up to the tile height 128 (256 for CTA pairs), C = NP/128):
+//   weights, forward  Wf [C*2*RB, NP] bf16 (RB = 208, or 224 when CTA pairs are used, i.e. B > 128): block (q,s) rows = {Wo[i,:], Wl[i,:], Wr[i,:] for the 64 neurons i of
 //                     sub-slice s of CTA q, a row of ones, zero rows}; columns j >= N zero
 //   weights, backward Wb, same shape: rows = {Wo[:,j], Wl[:,j], Wr[:,j] for the 64 neurons j, ones, zeros}
 //   saved             Rh [T+1][BP][NP] bf16 (Rh[0] = r_init, Rh[t+1] = r_t) | Dh [T][BP][NP] bf16 = F'(re_t)
@@ -18,21 +18,28 @@ using namespace tcr;
 
 struct TcFwdParams;
 struct TcBwdParams;
-int tc_forward_launch(int act, int NP, const CUtensorMap& tmW, const CUtensorMap& tmR0, const void* params,
+int tc_forward_launch(int act, int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmR0, const void* params,
                       cudaStream_t s);
-int tc_backward_launch(int NP, const CUtensorMap& tmW, const void* params, cudaStream_t s);
+int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const void* params, cudaStream_t s);
 __global__ void grad_j_kernel(const float* __restrict__ raw, const float* __restrict__ Wo, size_t NN, float* grad_J);
 
 namespace {
 
 int padded_n(int N) { return N <= 128 ? 128 : (N <= 256 ? 256 : (N <= 512 ? 512 : 0)); }
-int padded_b(int B) { return (B + 127) / 128 * 128; }
+// CTA pairs (tiles of 256 samples, cta_group::2 MMAs sharing every weight tile) halve the weight stream, but a B200
+// keeps at most 15 clusters of 8 CTAs resident against 33 clusters of 4, so for N = 512 the single shape finishes a
+// 4096-sample batch in one wave and pairs need two.  Pairs are therefore opt-in (RINGRNN_PAIRS=1), for experiments.
+bool use_pairs(int B) {
+  static const bool on = getenv("RINGRNN_PAIRS") != nullptr && getenv("RINGRNN_PAIRS")[0] == '1';
+  return on && B > 128;
+}
+int padded_b(int B) { return use_pairs(B) ? (B + 255) / 256 * 256 : (B + 127) / 128 * 128; }
 int n_active_of(const RingRnnProblem& p) { return p.n_active < 0 ? p.a_dim : p.n_active; }
 
 // Wf / Wb blocks, see the header comment.  grid (NP/64 column chunks, C*2 blocks), block 256
 __global__ void prep_weights_kernel(const float* __restrict__ Wo, const float* __restrict__ Wl,
-                                    const float* __restrict__ Wr, int N, int NP, __nv_bfloat16* __restrict__ Wf,
-                                    __nv_bfloat16* __restrict__ Wb) {
+                                    const float* __restrict__ Wr, int N, int NP, int RB,
+                                    __nv_bfloat16* __restrict__ Wf, __nv_bfloat16* __restrict__ Wb) {
   const int blk = blockIdx.y;  // q*2 + s
   const int n_first = blk * 64;
   for (int idx = threadIdx.x; idx < RB * 64; idx += blockDim.x) {
@@ -82,7 +89,8 @@ __global__ void dec_reduce_kernel(const float* __restrict__ part, int slots, int
 }
 
 struct Layout {
-  int NP, BP, C;
+  int NP, BP, C, RB, tile_rows;
+  bool pair;
   size_t w_bytes, r0_bytes, dec_bytes, state_bytes;
 };
 
@@ -91,7 +99,10 @@ Layout layout_of(const RingRnnProblem& p) {
   l.NP = padded_n(p.N);
   l.BP = padded_b(p.B);
   l.C = l.NP / 128;
-  l.w_bytes = align_up((size_t)l.C * 2 * RB * l.NP * 2, 1024);
+  l.pair = use_pairs(p.B);
+  l.RB = block_rows(l.pair);
+  l.tile_rows = l.pair ? 256 : 128;
+  l.w_bytes = align_up((size_t)l.C * 2 * l.RB * l.NP * 2, 1024);
   l.r0_bytes = align_up((size_t)l.BP * l.NP * 2, 1024);
   l.dec_bytes = align_up((size_t)2 * l.C * 3 * p.T * l.BP * 4, 1024);
   l.state_bytes = align_up((size_t)l.BP * l.NP * 2, 1024);  // one time slot of Rh / Dh
@@ -152,7 +163,7 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   const float* Wr = dp.n_mat > 2 ? dp.Wa + (size_t)dp.cols[1] * p.N * p.N : nullptr;
   {
     LaunchScope ls(K_PREP, s);
-    prep_weights_kernel<<<dim3(l.NP / 64, l.C * 2), 256, 0, s>>>(p.Wo, Wl, Wr, p.N, l.NP, Wf, nullptr);
+    prep_weights_kernel<<<dim3(l.NP / 64, l.C * 2), 256, 0, s>>>(p.Wo, Wl, Wr, p.N, l.NP, l.RB, Wf, nullptr);
   }
   RINGRNN_CUDA_TRY(cudaGetLastError());
   {
@@ -162,7 +173,8 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   RINGRNN_CUDA_TRY(cudaGetLastError());
 
   CUtensorMap tmW, tmR0;
-  if (!make_tmap_bf16_2d(&tmW, Wf, (uint64_t)l.C * 2 * RB, (uint64_t)l.NP, RB, 64)) return RINGRNN_ERR_CUDA;
+  if (!make_tmap_bf16_2d(&tmW, Wf, (uint64_t)l.C * 2 * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, 64))
+    return RINGRNN_ERR_CUDA;
   if (!make_tmap_bf16_2d(&tmR0, R0, (uint64_t)l.BP, (uint64_t)l.NP, 128, 64)) return RINGRNN_ERR_CUDA;
 
   const bool want_dec = a.dec_x || a.dec_y || a.dec_ta;
@@ -171,7 +183,7 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   fp.B = p.B; fp.T = p.T; fp.N = p.N; fp.BP = l.BP; fp.a_dim = p.a_dim;
   fp.colL = dp.n_mat > 1 ? dp.cols[0] : -1;
   fp.colR = dp.n_mat > 2 ? dp.cols[1] : -1;
-  fp.n_tiles = l.BP / 128;
+  fp.n_tiles = l.BP / l.tile_rows;
   fp.J0 = p.J0; fp.J1 = p.J1; fp.alpha = p.alpha;
   fp.A = p.A; fp.r_init = p.r_init;
   fp.Rh = Rh; fp.Dh = Dh;
@@ -180,7 +192,7 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   fp.dec_u = a.dec_u; fp.dec_v = a.dec_v;
   fp.final_state = a.final_state;
   fp.status = status;
-  int rc = tc_forward_launch(p.activation, l.NP, tmW, tmR0, &fp, s);
+  int rc = tc_forward_launch(p.activation, l.NP, l.pair, tmW, tmR0, &fp, s);
   if (rc != RINGRNN_OK) return rc;
   if (want_dec) {
     LaunchScope ls(K_LOSS, s);
@@ -288,17 +300,18 @@ int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   const int colL = dp.n_mat > 1 ? dp.cols[0] : -1, colR = dp.n_mat > 2 ? dp.cols[1] : -1;
   {
     LaunchScope ls(K_PREP, s);
-    prep_weights_kernel<<<dim3(l.NP / 64, l.C * 2), 256, 0, s>>>(p.Wo, Wl, Wr, p.N, l.NP, nullptr, Wb);
+    prep_weights_kernel<<<dim3(l.NP / 64, l.C * 2), 256, 0, s>>>(p.Wo, Wl, Wr, p.N, l.NP, l.RB, nullptr, Wb);
   }
   RINGRNN_CUDA_TRY(cudaGetLastError());
   CUtensorMap tmW;
-  if (!make_tmap_bf16_2d(&tmW, Wb, (uint64_t)l.C * 2 * RB, (uint64_t)l.NP, RB, 64)) return RINGRNN_ERR_CUDA;
+  if (!make_tmap_bf16_2d(&tmW, Wb, (uint64_t)l.C * 2 * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, 64))
+    return RINGRNN_ERR_CUDA;
 
   TcBwdParamsHost bp;
   memset(&bp, 0, sizeof(bp));
   bp.B = p.B; bp.T = p.T; bp.N = p.N; bp.BP = l.BP; bp.a_dim = p.a_dim;
   bp.colL = colL; bp.colR = colR;
-  bp.n_tiles = l.BP / 128;
+  bp.n_tiles = l.BP / l.tile_rows;
   bp.J0 = p.J0; bp.J1 = p.J1; bp.alpha = p.alpha;
   bp.A = p.A; bp.Rh = Rh; bp.Dh = Dh;
   bp.grad_output = a.grad_output;
@@ -307,7 +320,7 @@ int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   bp.DL = DL;
   bp.grad_r_init = a.grad_r_init;
   bp.status = status;
-  int rc = tc_backward_launch(l.NP, tmW, &bp, s);
+  int rc = tc_backward_launch(l.NP, l.pair, tmW, &bp, s);
   if (rc != RINGRNN_OK) return rc;
 
   // dWcat[3NP, NP] = DL^T [3NP, T*BP] x Rh[0..T) [T*BP, NP]

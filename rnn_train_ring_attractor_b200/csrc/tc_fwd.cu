@@ -3,7 +3,7 @@
 // fwd_wmma_kernel (cpp/kernels/fwd_1loop_tc_idx.cuh:265-277), which rebuild the per-sample effective
 // weight matrix on tensor cores and do the actual recurrence on CUDA cores.
 //
-// Per step and CTA:   D_s[128, 208] = r_{t-1}[128, NP] x Wblock_s^T      (s = 0, 1; fp32 in TMEM)
+// Per step and MMA unit:   D_s[128 or 256, RB] = r_{t-1}[.., NP] x Wblock_s^T      (s = 0, 1; fp32 in TMEM)
 // epilogue (thread = sample):   re = J0*S + J1*Yo + L*Yl + R*Yr,  r_t = (1-alpha) r_{t-1} + alpha F(re)
 // with the fp32 master copy of r in registers; bf16(r_t) goes to the A buffers of all CTAs of the cluster
 // for the next step, to the saved state, and F'(re) (bf16) to the saved derivative history; optional fp32
@@ -18,7 +18,7 @@ using namespace tc;
 using namespace tcr;
 
 struct TcFwdParams {
-  int B, T, N, BP, a_dim, colL, colR, n_tiles;
+  int B, T, N, BP, a_dim, colL, colR, n_tiles;  // n_tiles = BP / (128 or, for CTA pairs, 256)
   float J0, J1, alpha;
   const float* A;        // [B,T,a_dim]
   const float* r_init;   // [B,N]
@@ -32,143 +32,41 @@ struct TcFwdParams {
   int* status;
 };
 
-template <int ACT, int NP>
+template <int ACT, int NP, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmR0, const TcFwdParams p) {
-  using C_ = Cfg<NP>;
-  constexpr int C = C_::C, KC = C_::KC, NS = C_::NS;
-  constexpr bool RESIDENT = C_::RESIDENT;
+  using C_ = Cfg<NP, PAIR>;
+  constexpr int KC = C_::KC;
   extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t a_base = base;
-  const uint32_t w_base = base + C_::A_BYTES;
-  const uint32_t bars = w_base + NS * WT_BYTES;
-  uint8_t* bars_gen = gen + C_::A_BYTES + NS * WT_BYTES;
-  volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(bars_gen + OFF_TMEM_SLOT);
-  volatile int* dead = reinterpret_cast<volatile int*>(bars_gen + OFF_DEAD);
-  float* uv = reinterpret_cast<float*>(bars_gen + OFF_UV);
-  const WaitCtx wctx{dead, p.status};
-
+  const Ctx<NP, PAIR> c = setup_cta<NP, PAIR>(smem_raw, p.dec_u, p.dec_v, p.N, p.status);
+  const uint32_t a_base = c.a_base, bars = c.bars, tmem_base = c.tmem_base;
+  const WaitCtx& wctx = c.wctx;
+  float* uv = c.uv;
+  const int q = c.q;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t q = (C > 1) ? cluster_ctarank() : 0u;
-  const int cluster_id = blockIdx.x / C, n_clusters = gridDim.x / C;
+  const int cluster_id = blockIdx.x / C_::CL, n_clusters = gridDim.x / C_::CL;
   const int T = p.T;
-
-  if (threadIdx.x == 0) {
-    *dead = 0;
-    for (int i = 0; i < 16; ++i) {
-      mbar_init(bars + OFF_W_FULL + 8 * i, 1);
-      mbar_init(bars + OFF_W_EMPTY + 8 * i, 1);
-    }
-    for (int i = 0; i < 8; ++i) mbar_init(bars + OFF_A_FULL + 8 * i, 1);
-    mbar_init(bars + OFF_D_FULL, 1);
-    mbar_init(bars + OFF_D_FULL + 8, 1);
-    mbar_init(bars + OFF_D_EMPTY, 8);      // all eight epilogue warps drain each accumulator
-    mbar_init(bars + OFF_D_EMPTY + 8, 8);
-    mbar_init(bars + OFF_MMA_DONE, 1);
-    mbar_init(bars + OFF_ALL_FREE, C);
-    fence_mbar_init();
-  }
-  if (threadIdx.x < 256) {
-    const int i = threadIdx.x & 127, n = (int)q * 128 + i;
-    const float* src = (threadIdx.x < 128) ? p.dec_u : p.dec_v;
-    uv[threadIdx.x] = (src != nullptr && n < p.N) ? src[n] : 0.f;
-  }
-  if (warp == 1) tmem_alloc(bars + OFF_TMEM_SLOT, TMEM_COLS);
-  tcgen05_fence_before();
-  __syncthreads();
-  if (C > 1) {  // every CTA's barriers exist before any peer signals them
-    cluster_arrive();
-    cluster_wait();
-  }
-  tcgen05_fence_after();
-  const uint32_t tmem_base = *tmem_slot_p;
+  const int my_tiles = (p.n_tiles - cluster_id + n_clusters - 1) / n_clusters;
+  const uint32_t total_steps = (uint32_t)my_tiles * (uint32_t)T;
 
   if (warp < 4) {
     reg_dec<40>();
     if (warp == 0 && lane == 0) {
-      // ---------------- TMA producer: the weight stream ----------------
-      tma_prefetch_desc(&tmW);
-      uint32_t wcount = 0;
-      int it = 0;
-      for (int tile = cluster_id; tile < p.n_tiles; tile += n_clusters, ++it) {
-        if (RESIDENT) {
-          if (it == 0) {
-            for (int s = 0; s < 2; ++s)
-              for (int i = 0; i < KC; ++i) {
-                const int kc = (2 * (int)q + i) % KC, st = s * KC + i;
-                mbar_arrive_expect_tx(bars + OFF_W_FULL + 8 * st, WT_BYTES);
-                tma_load_2d(w_base + st * WT_BYTES, &tmW, bars + OFF_W_FULL + 8 * st, kc * 64, ((int)q * 2 + s) * RB);
-              }
-          }
-        } else {
-          for (int t = 0; t < T; ++t)
-            for (int s = 0; s < 2; ++s)
-              for (int i = 0; i < KC; ++i, ++wcount) {
-                const int kc = (2 * (int)q + i) % KC, st = wcount % NS;
-                if (wcount >= (uint32_t)NS) mbar_wait(bars + OFF_W_EMPTY + 8 * st, (wcount / NS - 1) & 1u, wctx, 202);
-                mbar_arrive_expect_tx(bars + OFF_W_FULL + 8 * st, WT_BYTES);
-                tma_load_2d(w_base + st * WT_BYTES, &tmW, bars + OFF_W_FULL + 8 * st, kc * 64, ((int)q * 2 + s) * RB);
-              }
-        }
-      }
+      producer_loop<NP, PAIR>(c, &tmW, total_steps, 202);
     } else if (warp == 1 && lane == 0) {
-      // ---------------- MMA issuer ----------------
-      constexpr uint32_t idesc = make_idesc_bf16(128, RB, 0, 0);
-      uint32_t wcount = 0, g = 0;
-      for (int tile = cluster_id; tile < p.n_tiles; tile += n_clusters) {
-        for (int t = 0; t < T; ++t, ++g) {
-          for (int s = 0; s < 2; ++s) {
-            if (g > 0) mbar_wait(bars + OFF_D_EMPTY + 8 * s, (g - 1) & 1u, wctx, 203);
-            tcgen05_fence_after();
-            for (int i = 0; i < KC; ++i) {
-              const int kc = (2 * (int)q + i) % KC;
-              if (s == 0) {
-                mbar_wait(bars + OFF_A_FULL + 8 * kc, g & 1u, wctx, 204);
-                // chunks owned by peers arrive as bulk copies: arm the byte count of the next step's copy
-                if ((kc >> 1) != (int)q && t + 1 < T) mbar_arrive_expect_tx(bars + OFF_A_FULL + 8 * kc, CHUNK_BYTES);
-              }
-              int st;
-              if (RESIDENT) {
-                st = s * KC + i;
-                if (g == 0) mbar_wait(bars + OFF_W_FULL + 8 * st, 0, wctx, 205);
-              } else {
-                st = wcount % NS;
-                mbar_wait(bars + OFF_W_FULL + 8 * st, (wcount / NS) & 1u, wctx, 205);
-              }
-              tcgen05_fence_after();
-              const uint32_t a_src = a_base + kc * CHUNK_BYTES, b_src = w_base + st * WT_BYTES;
-#pragma unroll
-              for (int ks = 0; ks < 4; ++ks)
-                umma_ss(tmem_base + s * 256, make_smem_desc(a_src + ks * 32, 16, 1024),
-                        make_smem_desc(b_src + ks * 32, 16, 1024), idesc, (i > 0 || ks > 0) ? 1u : 0u);
-              if (!RESIDENT) {
-                umma_commit(bars + OFF_W_EMPTY + 8 * st);
-                ++wcount;
-              }
-            }
-            umma_commit(bars + OFF_D_FULL + 8 * s);
-          }
-          umma_commit(bars + OFF_MMA_DONE);
-        }
-      }
+      if (c.leader) mma_loop<NP, PAIR, true>(c, total_steps, T, 210);
     } else if (warp == 2 && lane == 0) {
-      // ---------------- relay: loads the initial state of each tile; after every step tells every CTA of the
-      // cluster that this CTA no longer reads its A buffer (it follows every phase of mma_done, so it is
-      // also the one that knows when the buffer may take the next tile) ----------------
       tma_prefetch_desc(&tmR0);
-      uint32_t g = 0;
-      for (int tile = cluster_id; tile < p.n_tiles; tile += n_clusters) {
+      relay_loop<NP, PAIR, true>(c, total_steps, T, 220, [&](int it) {
+        // initial state of the tile: this CTA's 128 samples, all K chunks (the previous tile's MMAs are done:
+        // the relay has seen every phase of mma_done)
+        const int tile = cluster_id + it * n_clusters;
         for (int kc = 0; kc < KC; ++kc) {
           mbar_arrive_expect_tx(bars + OFF_A_FULL + 8 * kc, CHUNK_BYTES);
-          tma_load_2d(a_base + kc * CHUNK_BYTES, &tmR0, bars + OFF_A_FULL + 8 * kc, kc * 64, tile * 128);
+          tma_load_2d(a_base + kc * CHUNK_BYTES, &tmR0, bars + OFF_A_FULL + 8 * kc, kc * 64,
+                      tile * C_::TILE_ROWS + c.half * 128);
         }
-        for (int t = 0; t < T; ++t, ++g) {
-          mbar_wait(bars + OFF_MMA_DONE, g & 1u, wctx, 206);
-          for (uint32_t r = 0; r < (uint32_t)C; ++r) mbar_arrive_cluster(bars + OFF_ALL_FREE, r);
-        }
-      }
+      });
     }
   } else {
     reg_inc<232>();
@@ -179,13 +77,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     const int h = (warp - 4) >> 2, quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const int nq = (int)q * 128 + 32 * h;  // neuron of master[0]; sub-slice s adds 64*s
-    const int slot = 2 * (int)q + h;
+    const int nq = q * 128 + 32 * h;  // neuron of master[0]; sub-slice s adds 64*s
+    const int slot = 2 * q + h;
     const float J0 = p.J0, J1 = p.J1, alpha = p.alpha, beta = 1.f - p.alpha;
     const bool want_dec = p.dec_part != nullptr;
     uint32_t g = 0;
     for (int tile = cluster_id; tile < p.n_tiles; tile += n_clusters) {
-      const int b = tile * 128 + row;
+      const int b = tile * C_::TILE_ROWS + c.half * 128 + row;
       const bool valid = b < p.B;
       float master[64];
 #pragma unroll
@@ -207,6 +105,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
           mbar_wait(bars + OFF_D_FULL + 8 * s, g & 1u, wctx, 207);
+          if (warp == 4 && lane == 0) RINGRNN_STAMP(g, s == 0 ? 5 : 7);
           tcgen05_fence_after();
           uint32_t yo[32], yl[32], yr[32];
           const uint32_t col = tmem_base + lane_base + s * 256 + 32 * h;
@@ -224,10 +123,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             tmem_ld32(col + 128, yr);
             tmem_ld_wait();
           }
-          // the accumulator is in registers: hand it back to the MMA warp
-          tcgen05_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bars + OFF_D_EMPTY + 8 * s);
+          release_accumulator<NP, PAIR>(c, s, lane);  // the accumulator is in registers: hand it back
+          if (warp == 4 && lane == 0) RINGRNN_STAMP(g, s == 0 ? 6 : 8);
           uint32_t dpk[16];
 #pragma unroll
           for (int j0 = 0; j0 < 32; j0 += 8) {
@@ -266,34 +163,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         }
         // every CTA of the cluster has finished reading r_{t-1} (waited for in every step so that no phase of
         // the barrier is skipped); then publish r_t
+        if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 9);
         mbar_wait<true>(bars + OFF_ALL_FREE, g & 1u, wctx, 208);
-        if (t + 1 < T) {
-#pragma unroll
-          for (int s = 0; s < 2; ++s) {
-            const uint32_t tile_addr = a_base + (2 * (int)q + s) * CHUNK_BYTES;
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              const uint32_t unit = (uint32_t)(4 * h + v);
-              const uint32_t addr = tile_addr + row * 128 + ((unit ^ ((uint32_t)row & 7u)) << 4);
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[s * 16 + 4 * v]),
-                           "r"(packed[s * 16 + 4 * v + 1]), "r"(packed[s * 16 + 4 * v + 2]),
-                           "r"(packed[s * 16 + 4 * v + 3])
-                           : "memory");
-            }
-          }
-          fence_proxy_async_smem();
-          named_bar_sync(1, 256);
-          if (warp == 4 && lane == 0) {
-#pragma unroll
-            for (int s = 0; s < 2; ++s) {
-              const int kc = 2 * (int)q + s;
-              const uint32_t tile_addr = a_base + kc * CHUNK_BYTES;
-              mbar_arrive(bars + OFF_A_FULL + 8 * kc);
-              for (uint32_t r = 0; r < (uint32_t)C; ++r)
-                if (r != q) dsmem_bulk_copy(tile_addr, tile_addr, CHUNK_BYTES, bars + OFF_A_FULL + 8 * kc, r);
-            }
-          }
-        }
+        if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 10);
+        if (t + 1 < T) publish_chunks<NP, PAIR>(c, packed, row, h, warp, lane);
+        if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 11);
         // off the critical path: saved state, fp32 history, decode sums
         if (p.Rh != nullptr) {
 #pragma unroll
@@ -338,47 +212,41 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       }
     }
   }
-  // ---------------- teardown: nobody leaves while a peer may still signal or copy into this CTA ----------------
-  tcgen05_fence_before();
-  __syncthreads();
-  if (C > 1) {
-    cluster_arrive();
-    cluster_wait();
-  }
-  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  teardown_cta<NP, PAIR>(c);
 }
 
-template <int ACT, int NP>
+template <int ACT, int NP, bool PAIR>
 static int launch_fwd_tc(const CUtensorMap& tmW, const CUtensorMap& tmR0, const TcFwdParams& p, cudaStream_t s) {
-  using C_ = Cfg<NP>;
-  RINGRNN_CUDA_TRY(cudaFuncSetAttribute(fwd_tc_kernel<ACT, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM));
-  int max_clusters = 148 / C_::C;
-  int n_clusters = p.n_tiles < max_clusters ? p.n_tiles : max_clusters;
+  using C_ = Cfg<NP, PAIR>;
+  auto kernel = fwd_tc_kernel<ACT, NP, PAIR>;
+  RINGRNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM));
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(n_clusters * C_::C, 1, 1);
   cfg.blockDim = dim3(THREADS, 1, 1);
   cfg.dynamicSmemBytes = C_::SMEM;
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = C_::C;
+  attr[0].val.clusterDim.x = C_::CL;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  const int n_clusters = clusters_to_launch(reinterpret_cast<const void*>(kernel), &cfg, C_::CL, p.n_tiles);
+  cfg.gridDim = dim3(n_clusters * C_::CL, 1, 1);
   {
     LaunchScope ls(K_FWD, s);
-    RINGRNN_CUDA_TRY(cudaLaunchKernelEx(&cfg, fwd_tc_kernel<ACT, NP>, tmW, tmR0, p));
+    RINGRNN_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmW, tmR0, p));
   }
   return RINGRNN_OK;
 }
 
-int tc_forward_launch(int act, int NP, const CUtensorMap& tmW, const CUtensorMap& tmR0, const void* params,
+int tc_forward_launch(int act, int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmR0, const void* params,
                       cudaStream_t s) {
   const TcFwdParams& p = *static_cast<const TcFwdParams*>(params);  // same field order as the host-side mirror
-#define RINGRNN_TCF(ACT, NPV) \
-  if (act == ACT && NP == NPV) return launch_fwd_tc<ACT, NPV>(tmW, tmR0, p, s);
+#define RINGRNN_TCF(ACT, NPV)                                                              \
+  if (act == ACT && NP == NPV)                                                             \
+    return pair ? launch_fwd_tc<ACT, NPV, true>(tmW, tmR0, p, s) : launch_fwd_tc<ACT, NPV, false>(tmW, tmR0, p, s);
   RINGRNN_TCF(RINGRNN_ACT_RELU, 128) RINGRNN_TCF(RINGRNN_ACT_RELU, 256) RINGRNN_TCF(RINGRNN_ACT_RELU, 512)
   RINGRNN_TCF(RINGRNN_ACT_GELU, 128) RINGRNN_TCF(RINGRNN_ACT_GELU, 256) RINGRNN_TCF(RINGRNN_ACT_GELU, 512)
   RINGRNN_TCF(RINGRNN_ACT_TANH, 128) RINGRNN_TCF(RINGRNN_ACT_TANH, 256) RINGRNN_TCF(RINGRNN_ACT_TANH, 512)
@@ -388,3 +256,9 @@ int tc_forward_launch(int act, int NP, const CUtensorMap& tmW, const CUtensorMap
 }
 
 }  // namespace ringrnn
+
+#ifdef RINGRNN_TIMELINE
+extern "C" int ringrnn_debug_timeline_read(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, ringrnn::g_timeline, sizeof(long long) * 64 * 16);
+}
+#endif

@@ -146,18 +146,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tcgen05_fence_after();
         const uint32_t a_src = base + s * Cfg::STAGE, b_src = a_src + Cfg::A_BYTES;
         constexpr int KSTEPS = Cfg::KC / 16;
+        const uint32_t a_lo = desc_lo(a_src, MN_MAJOR ? Cfg::KC * 128 : 16);
+        const uint32_t b_lo = desc_lo(b_src, MN_MAJOR ? Cfg::KC * 128 : 16);
+        constexpr uint32_t KSTEP_LO = MN_MAJOR ? (2048u >> 4) : (32u >> 4);
+        constexpr uint32_t NH_LO = MN_MAJOR ? ((4u * Cfg::KC * 128u) >> 4) : ((256u * 128u) >> 4);
+#pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
-          for (int nh = 0; nh < Cfg::NI; ++nh) {
-            uint64_t da, db;
-            if (MN_MAJOR) {
-              da = make_smem_desc(a_src + ks * 2048, Cfg::KC * 128, 1024);
-              db = make_smem_desc(b_src + nh * 4 * Cfg::KC * 128 + ks * 2048, Cfg::KC * 128, 1024);
-            } else {
-              da = make_smem_desc(a_src + ks * 32, 16, 1024);
-              db = make_smem_desc(b_src + nh * 256 * 128 + ks * 32, 16, 1024);
-            }
-            umma_ss(tmem_base + nh * 256, da, db, idesc, (it > 0 || ks > 0) ? 1u : 0u);
-          }
+#pragma unroll
+          for (int nh = 0; nh < Cfg::NI; ++nh)
+            umma_ss_lo(tmem_base + nh * 256, a_lo + ks * KSTEP_LO, b_lo + nh * NH_LO + ks * KSTEP_LO, idesc,
+                       (it > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(empty_bar(s));  // frees the stage when these MMAs have read it
       }
@@ -276,9 +274,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t a_src = base + s * Cfg::STAGE, b_src = a_src + Cfg::A_BYTES;
-        for (int ks = 0; ks < 4; ++ks)
-          umma_ss_pair(tmem_base, make_smem_desc(a_src + ks * 32, 16, 1024), make_smem_desc(b_src + ks * 32, 16, 1024),
-                       idesc, (it > 0 || ks > 0) ? 1u : 0u);
+        const uint32_t a_lo = desc_lo(a_src, 16), b_lo = desc_lo(b_src, 16);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) umma_ss_pair_lo(tmem_base, a_lo + 2 * ks, b_lo + 2 * ks, idesc, (it > 0 || ks > 0) ? 1u : 0u);
         umma_commit_pair(empty_bar(s), 3);
       }
       umma_commit_pair(done_bar, 3);

@@ -91,6 +91,9 @@ struct WaitCtx {
 // Waits for the phase with the given parity.  Returns false if the wait was abandoned.
 template <bool CLUSTER_ACQUIRE = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w, int code) {
+  // fast path: the phase is already complete (the common case for the single thread that issues the MMAs, whose
+  // instruction rate bounds the kernels)
+  if (CLUSTER_ACQUIRE ? mbar_try_wait_cluster_acquire(bar, parity) : mbar_try_wait(bar, parity)) return true;
   if (*w.dead) return false;
   const long long t0 = clock64();
   uint32_t spins = 0;
@@ -292,6 +295,42 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
   d |= (uint64_t)2 << 61;
   return d;
 }
+// The same descriptor split in halves so that the issuing thread spends a few instructions per MMA: the upper
+// 32 bits are constant (SBO = 1024, version, swizzle mode), the lower 32 bits are address >> 4 plus LBO >> 4 at bit 16;
+// stepping along K inside a K-major tile adds 2 (32 bytes) to the lower half, along an MN-major tile 128 (2048 bytes).
+constexpr uint32_t DESC_HI_SW128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
+}
+__device__ __forceinline__ void umma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(DESC_HI_SW128), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ss_pair_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(DESC_HI_SW128), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // Instruction descriptor, kind::f16: D fp32 (bits [4,6) = 1), A and B bf16 (bits [7,10) = [10,13) = 1),
 // bit 15 / 16 = A / B is MN-major, N >> 3 at [17,23), M >> 4 at [24,29).
 __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn_major, int b_mn_major) {

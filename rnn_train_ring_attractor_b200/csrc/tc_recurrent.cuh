@@ -1,62 +1,100 @@
 // Shared definitions of the bf16 tensor-core recurrent kernels (forward and reverse-time).
 //
-// Decomposition.  The padded neuron count NP (128, 256 or 512) is split over a thread-block cluster of
-// C = NP/128 CTAs; a cluster owns one tile of 128 samples at a time and runs all its timesteps.  CTA q of the
-// cluster produces neurons [128q, 128q+128) in two sub-slices of 64.  Per step every CTA needs the whole
-// previous state as the A operand [128 samples x NP] (bf16, K-major, 128-byte swizzle, one 16 KB chunk per
-// 64 neurons); the weights for its own output neurons are the B operand, streamed by TMA through a ring of
+// Decomposition.  The padded neuron count NP (128, 256 or 512) is split into C = NP/128 slices of 128 neurons.
+// A thread-block cluster owns one tile of samples at a time and runs all its timesteps; the CTA that owns
+// slice q produces neurons [128q, 128q+128) in two sub-slices of 64.  Per step a CTA needs the whole previous
+// state of its 128 samples as the A operand [128 x NP] (bf16, K-major, 128-byte swizzle, one 16 KB chunk per
+// 64 neurons); the weights of its output neurons are the B operand, streamed by TMA through a ring of
 // shared-memory stages (or loaded once when they fit).  After the epilogue each CTA pushes its two new
-// 64-neuron chunks into every peer's A buffer with one-destination bulk copies over distributed shared
-// memory; mbarriers carry the byte counts.
+// 64-neuron chunks into the A buffers of the CTAs that hold the same samples, with one-destination bulk copies
+// over distributed shared memory; mbarriers carry the byte counts.
 //
-// Weight blocks.  For CTA q, sub-slice s the B operand is a block of RB = 208 rows x NP columns:
+// Two cluster shapes:
+//   single (PAIR = false): C CTAs, 128 samples, each CTA issues its own tcgen05.mma (M = 128, N = 208).
+//   pair   (PAIR = true) : 2C CTAs, 256 samples.  Ranks (2q, 2q+1) hold slice q for the two halves of the samples
+//          and act as one cta_group::2 MMA unit (M = 256, N = 224): each loads only half of every weight tile,
+//          which halves both the L2 -> shared-memory stream and the shared-memory traffic per MMA, the two
+//          things that bound the single shape.  The even CTA issues the MMAs; completions are signalled to both.
+//
+// Weight blocks.  For slice q, sub-slice s the B operand is a block of RB rows x NP columns:
 //   rows   0.. 63  matrix 0 (Wo)   rows 64..127  matrix 1 (Wl)   rows 128..191  matrix 2 (Wr)
 //   row  192       ones (for columns < N): its accumulator column is the row sum of the A operand,
-//                  which the J0 (global inhibition) term needs;  rows 193..207 zero.
-// One tcgen05.mma with N = 208 therefore yields, per sample, the three 64-wide products and the row sum.
+//                  which the J0 (global inhibition) term needs;  remaining rows zero (RB = 208, or 224 for pairs,
+//                  whose MMA wants N to be a multiple of 32).
+// One MMA therefore yields, per sample, the three 64-wide products and the row sum.
 #pragma once
 
 #include <cuda_bf16.h>
+#include <stdio.h>
+#include <stdlib.h>
 
 #include "ringrnn_common.cuh"
 #include "tc_ptx.cuh"
 
 namespace ringrnn {
+
+// Optional in-kernel timeline (compile with -DRINGRNN_TIMELINE): cycle stamps of CTA `RINGRNN_TIMELINE_CTA` for the
+// first 64 steps, 16 slots per step, read back with ringrnn_debug_timeline_read().  Compiled out by default.
+#ifdef RINGRNN_TIMELINE
+static __device__ long long g_timeline[64 * 16];  // one copy per translation unit
+#ifndef RINGRNN_TIMELINE_CTA
+#define RINGRNN_TIMELINE_CTA 8
+#endif
+#define RINGRNN_STAMP(step, slot)                                                                   \
+  do {                                                                                              \
+    if (blockIdx.x == RINGRNN_TIMELINE_CTA && (step) < 64) g_timeline[(step) * 16 + (slot)] = clock64(); \
+  } while (0)
+#define RINGRNN_STAMP_VAL(step, slot, v)                                                            \
+  do {                                                                                              \
+    if (blockIdx.x == RINGRNN_TIMELINE_CTA && (step) < 64) g_timeline[(step) * 16 + (slot)] = (v);  \
+  } while (0)
+#else
+#define RINGRNN_STAMP(step, slot) do {} while (0)
+#define RINGRNN_STAMP_VAL(step, slot, v) do {} while (0)
+#endif
+
 namespace tcr {
 
-constexpr int RB = 208;              // rows of one weight block
-constexpr int WT_BYTES = RB * 128;   // one [RB x 64] bf16 tile
 constexpr int CHUNK_BYTES = 128 * 128;  // one [128 samples x 64 neurons] bf16 chunk
 constexpr int THREADS = 384;         // warps 0-3: TMA / MMA / relay / idle; warps 4-11: epilogue
 constexpr int SMEM_LIMIT = 232448;   // 227 KB
 constexpr int TMEM_COLS = 512;
 constexpr int SUM_COL = 192;
 
-template <int NP>
+constexpr int block_rows(bool pair) { return pair ? 224 : 208; }
+
+template <int NP, bool PAIR>
 struct Cfg {
-  static constexpr int C = NP / 128;   // CTAs per cluster
-  static constexpr int KC = NP / 64;   // K chunks
+  static constexpr int C = NP / 128;             // neuron slices
+  static constexpr int CL = PAIR ? 2 * C : C;    // CTAs per cluster
+  static constexpr int TILE_ROWS = PAIR ? 256 : 128;
+  static constexpr int KC = NP / 64;             // K chunks
+  static constexpr int RB = block_rows(PAIR);    // rows of one weight block = accumulator columns used
+  static constexpr int WROWS = PAIR ? RB / 2 : RB;  // rows of a weight tile this CTA loads
+  static constexpr int WT_BYTES = WROWS * 128;   // one [WROWS x 64] bf16 tile
   static constexpr int A_BYTES = KC * CHUNK_BYTES;
-  static constexpr int TILES = 2 * KC;  // weight tiles per step
-  static constexpr int AUX = 2048;      // barriers, flags, decode vectors
+  static constexpr int TILES = 2 * KC;           // weight tiles per step
+  static constexpr int AUX = 2048;               // barriers, flags, decode vectors
   static constexpr int NS_FIT = (SMEM_LIMIT - 1024 - AUX - A_BYTES) / WT_BYTES;
   static constexpr bool RESIDENT = NS_FIT >= TILES;
-  static constexpr int NS = RESIDENT ? TILES : NS_FIT;
+  static constexpr int NS = RESIDENT ? TILES : (NS_FIT > 16 ? 16 : NS_FIT);
   static constexpr int SMEM = 1024 + A_BYTES + NS * WT_BYTES + AUX;
   static_assert(NS >= 2, "weight ring too small");
   static_assert(NS <= 16, "barrier block sized for 16 stages");
+  static_assert(WT_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
 };
 
 // barrier block: byte offsets from its base
 constexpr uint32_t OFF_W_FULL = 0;     // [16]
 constexpr uint32_t OFF_W_EMPTY = 128;  // [16]
-constexpr uint32_t OFF_A_FULL = 256;   // [8]
+constexpr uint32_t OFF_A_FULL = 256;   // [8]  chunk kc of this CTA's A buffer is complete
 constexpr uint32_t OFF_D_FULL = 320;   // [2]
 constexpr uint32_t OFF_D_EMPTY = 336;  // [2]
 constexpr uint32_t OFF_MMA_DONE = 352;
 constexpr uint32_t OFF_ALL_FREE = 360;
 constexpr uint32_t OFF_TMEM_SLOT = 368;
 constexpr uint32_t OFF_DEAD = 372;
+constexpr uint32_t OFF_A_PAIR = 384;   // [8]  (even CTA of a pair) chunk kc is complete in the odd CTA too
 constexpr uint32_t OFF_UV = 512;       // float u[128], v[128]
 
 template <int REGS>
@@ -130,5 +168,309 @@ __device__ __forceinline__ void act_group(const float* x, float* f, float* d) {
   }
 }
 
+
+// ---- per-CTA context and the roles both directions share -------------------------------------------------------
+template <int NP, bool PAIR>
+struct Ctx {
+  uint32_t a_base, w_base, bars, tmem_base;
+  int q;            // neuron slice of this CTA
+  int half;         // which 128 of the tile's samples (always 0 in the single shape)
+  bool leader;      // issues the MMAs (every CTA in the single shape, the even CTA of a pair otherwise)
+  uint32_t rank, leader_rank;
+  uint16_t pair_mask;  // cluster ranks of this CTA's MMA unit
+  float* uv;
+  tc::WaitCtx wctx;
+  __device__ __forceinline__ uint32_t peer_rank(int q2) const { return PAIR ? (uint32_t)(2 * q2 + half) : (uint32_t)q2; }
+};
+
+// Barrier init, TMEM allocation, decode vectors, cluster-wide start line.
+template <int NP, bool PAIR>
+__device__ __forceinline__ Ctx<NP, PAIR> setup_cta(uint8_t* smem_raw, const float* dec_u, const float* dec_v, int N,
+                                                    int* status) {
+  using C_ = Cfg<NP, PAIR>;
+  using namespace tc;
+  Ctx<NP, PAIR> c;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  c.a_base = base;
+  c.w_base = base + C_::A_BYTES;
+  c.bars = c.w_base + C_::NS * C_::WT_BYTES;
+  uint8_t* bars_gen = gen + C_::A_BYTES + C_::NS * C_::WT_BYTES;
+  volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(bars_gen + OFF_TMEM_SLOT);
+  volatile int* dead = reinterpret_cast<volatile int*>(bars_gen + OFF_DEAD);
+  c.uv = reinterpret_cast<float*>(bars_gen + OFF_UV);
+  c.wctx = WaitCtx{dead, status};
+  c.rank = (C_::CL > 1) ? cluster_ctarank() : 0u;
+  c.q = PAIR ? (int)(c.rank >> 1) : (int)c.rank;
+  c.half = PAIR ? (int)(c.rank & 1u) : 0;
+  c.leader = c.half == 0;
+  c.leader_rank = PAIR ? (c.rank & ~1u) : c.rank;
+  c.pair_mask = (uint16_t)(3u << (2 * c.q));
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    *dead = 0;
+    for (int i = 0; i < 16; ++i) {
+      mbar_init(c.bars + OFF_W_FULL + 8 * i, 1);
+      mbar_init(c.bars + OFF_W_EMPTY + 8 * i, 1);
+    }
+    for (int i = 0; i < 8; ++i) {
+      mbar_init(c.bars + OFF_A_FULL + 8 * i, 1);
+      mbar_init(c.bars + OFF_A_PAIR + 8 * i, 1);
+    }
+    mbar_init(c.bars + OFF_D_FULL, 1);
+    mbar_init(c.bars + OFF_D_FULL + 8, 1);
+    mbar_init(c.bars + OFF_D_EMPTY, PAIR ? 16 : 8);  // every epilogue warp of the MMA unit drains each accumulator
+    mbar_init(c.bars + OFF_D_EMPTY + 8, PAIR ? 16 : 8);
+    mbar_init(c.bars + OFF_MMA_DONE, 1);
+    mbar_init(c.bars + OFF_ALL_FREE, C_::C);
+    fence_mbar_init();
+  }
+  if (threadIdx.x < 256) {
+    const int i = threadIdx.x & 127, n = c.q * 128 + i;
+    const float* src = (threadIdx.x < 128) ? dec_u : dec_v;
+    c.uv[threadIdx.x] = (src != nullptr && n < N) ? src[n] : 0.f;
+  }
+  if (warp == 1) {
+    if (PAIR) tmem_alloc_pair(c.bars + OFF_TMEM_SLOT, TMEM_COLS);
+    else tmem_alloc(c.bars + OFF_TMEM_SLOT, TMEM_COLS);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (C_::CL > 1) {  // every CTA's barriers exist before any peer signals them
+    cluster_arrive();
+    cluster_wait();
+  }
+  tcgen05_fence_after();
+  c.tmem_base = *tmem_slot_p;
+  return c;
+}
+
+template <int NP, bool PAIR>
+__device__ __forceinline__ void teardown_cta(const Ctx<NP, PAIR>& c) {
+  using namespace tc;
+  // nobody leaves while a peer may still signal or copy into this CTA
+  tcgen05_fence_before();
+  __syncthreads();
+  if (Cfg<NP, PAIR>::CL > 1) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  if ((threadIdx.x >> 5) == 1) {
+    if (PAIR) tmem_dealloc_pair(c.tmem_base, TMEM_COLS);
+    else tmem_dealloc(c.tmem_base, TMEM_COLS);
+  }
+}
+
+// Weight stream (one thread per CTA).  Tile order per step: sub-slice 0 then 1, K chunks starting at this slice's own.
+template <int NP, bool PAIR>
+__device__ __forceinline__ void producer_loop(const Ctx<NP, PAIR>& c, const CUtensorMap* tmW, uint32_t total_steps,
+                                              int code) {
+  using C_ = Cfg<NP, PAIR>;
+  using namespace tc;
+  constexpr int KC = C_::KC, NS = C_::NS;
+  tma_prefetch_desc(tmW);
+  if (total_steps == 0) return;
+  auto issue = [&](int st, int s, int kc) {
+    const uint32_t bar = c.bars + OFF_W_FULL + 8 * st;
+    const int y = (c.q * 2 + s) * C_::RB + c.half * C_::WROWS;
+    if (c.leader) mbar_arrive_expect_tx(bar, (PAIR ? 2 : 1) * C_::WT_BYTES);  // a pair's two halves land on one barrier
+    if (PAIR) tma_load_2d_pair(c.w_base + st * C_::WT_BYTES, tmW, bar, kc * 64, y);
+    else tma_load_2d(c.w_base + st * C_::WT_BYTES, tmW, bar, kc * 64, y);
+  };
+  if (C_::RESIDENT) {
+    for (int s = 0; s < 2; ++s)
+      for (int i = 0; i < KC; ++i) issue(s * KC + i, s, (2 * c.q + i) % KC);
+  } else {
+    uint32_t wcount = 0;
+    for (uint32_t g = 0; g < total_steps; ++g)
+      for (int s = 0; s < 2; ++s)
+        for (int i = 0; i < KC; ++i, ++wcount) {
+          const int st = wcount % NS;
+          if (wcount >= (uint32_t)NS) mbar_wait(c.bars + OFF_W_EMPTY + 8 * st, (wcount / NS - 1) & 1u, c.wctx, code);
+          issue(st, s, (2 * c.q + i) % KC);
+        }
+  }
+}
+
+// Should the byte count of the copy that will bring chunk kc for step g+1 be armed after step g's wait?
+// Forward: the first step of every tile is loaded by TMA instead (armed there); reverse: every step but the last.
+template <bool FWD>
+__device__ __forceinline__ bool arm_next(uint32_t g, uint32_t total_steps, int T) {
+  return FWD ? ((int)(g % (uint32_t)T) + 1 < T) : (g + 1 < total_steps);
+}
+
+// MMA issuer (one thread of the leader CTA).
+template <int NP, bool PAIR, bool FWD>
+__device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_steps, int T, int code) {
+  using C_ = Cfg<NP, PAIR>;
+  using namespace tc;
+  constexpr int KC = C_::KC, NS = C_::NS;
+  constexpr uint32_t idesc = make_idesc_bf16(PAIR ? 256 : 128, C_::RB, 0, 0);
+  uint32_t wcount = 0;
+  if (!FWD && total_steps > 0)  // reverse: nothing loads the first A operand by TMA, peers push it
+    for (int kc = 0; kc < KC; ++kc)
+      if ((kc >> 1) != c.q) mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * kc, CHUNK_BYTES);
+  auto commit = [&](uint32_t bar) {
+    if (PAIR) umma_commit_pair(bar, c.pair_mask);
+    else umma_commit(bar);
+  };
+  for (uint32_t g = 0; g < total_steps; ++g) {
+#ifdef RINGRNN_TIMELINE
+    long long acc_w = 0, acc_a = 0, acc_p = 0, t0;
+#endif
+    for (int s = 0; s < 2; ++s) {
+      if (g > 0) mbar_wait<PAIR>(c.bars + OFF_D_EMPTY + 8 * s, (g - 1) & 1u, c.wctx, code + 0);
+      RINGRNN_STAMP(g, s == 0 ? 0 : 2);
+      tcgen05_fence_after();
+      for (int i = 0; i < KC; ++i) {
+        const int kc = (2 * c.q + i) % KC;
+        if (s == 0) {
+#ifdef RINGRNN_TIMELINE
+          t0 = clock64();
+#endif
+          mbar_wait(c.bars + OFF_A_FULL + 8 * kc, g & 1u, c.wctx, code + 1);
+#ifdef RINGRNN_TIMELINE
+          acc_a += clock64() - t0;
+          t0 = clock64();
+#endif
+          // chunks owned by other slices arrive as bulk copies: arm the byte count of the next step's copy
+          if ((kc >> 1) != c.q && arm_next<FWD>(g, total_steps, T))
+            mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * kc, CHUNK_BYTES);
+          if (PAIR) mbar_wait<true>(c.bars + OFF_A_PAIR + 8 * kc, g & 1u, c.wctx, code + 2);
+#ifdef RINGRNN_TIMELINE
+          acc_p += clock64() - t0;
+          if (i == 1) RINGRNN_STAMP(g, 1);
+#endif
+        }
+        int st;
+        if (C_::RESIDENT) {
+          st = s * KC + i;
+          if (g == 0) mbar_wait(c.bars + OFF_W_FULL + 8 * st, 0, c.wctx, code + 3);
+        } else {
+          st = wcount % NS;
+#ifdef RINGRNN_TIMELINE
+          t0 = clock64();
+#endif
+          mbar_wait(c.bars + OFF_W_FULL + 8 * st, (wcount / NS) & 1u, c.wctx, code + 3);
+#ifdef RINGRNN_TIMELINE
+          acc_w += clock64() - t0;
+#endif
+        }
+        tcgen05_fence_after();
+        const uint32_t a_lo = desc_lo(c.a_base + kc * CHUNK_BYTES, 16), b_lo = desc_lo(c.w_base + st * C_::WT_BYTES, 16);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          if (PAIR) umma_ss_pair_lo(c.tmem_base + s * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc, (i > 0 || ks > 0) ? 1u : 0u);
+          else umma_ss_lo(c.tmem_base + s * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc, (i > 0 || ks > 0) ? 1u : 0u);
+        }
+        if (!C_::RESIDENT) {
+          commit(c.bars + OFF_W_EMPTY + 8 * st);
+          ++wcount;
+        }
+      }
+      commit(c.bars + OFF_D_FULL + 8 * s);
+      RINGRNN_STAMP(g, s == 0 ? 3 : 4);
+    }
+    commit(c.bars + OFF_MMA_DONE);
+#ifdef RINGRNN_TIMELINE
+    RINGRNN_STAMP_VAL(g, 13, acc_w);
+    RINGRNN_STAMP_VAL(g, 14, acc_a);
+    RINGRNN_STAMP_VAL(g, 15, acc_p);
+#endif
+  }
+}
+
+// Relay (one thread per CTA): follows every phase of mma_done.  The leader then tells every CTA of the cluster that
+// its MMA unit no longer reads the A buffers of step g; the odd CTA of a pair forwards "chunk kc is complete here"
+// to its leader and arms its own incoming copies.  `tile_start(tile_index)` runs before the first step of each tile
+// (forward: TMA load of the initial state into this CTA's A buffer).
+template <int NP, bool PAIR, bool FWD, class TileStart>
+__device__ __forceinline__ void relay_loop(const Ctx<NP, PAIR>& c, uint32_t total_steps, int T, int code,
+                                           TileStart tile_start) {
+  using C_ = Cfg<NP, PAIR>;
+  using namespace tc;
+  constexpr int KC = C_::KC;
+  if (PAIR && !c.leader && !FWD && total_steps > 0)
+    for (int kc = 0; kc < KC; ++kc)
+      if ((kc >> 1) != c.q) mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * kc, CHUNK_BYTES);
+  for (uint32_t g = 0; g < total_steps; ++g) {
+    if (g % (uint32_t)T == 0) tile_start((int)(g / (uint32_t)T));
+    if (PAIR && !c.leader) {
+      for (int i = 0; i < KC; ++i) {
+        const int kc = (2 * c.q + i) % KC;
+        mbar_wait(c.bars + OFF_A_FULL + 8 * kc, g & 1u, c.wctx, code + 0);
+        if ((kc >> 1) != c.q && arm_next<FWD>(g, total_steps, T))
+          mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * kc, CHUNK_BYTES);
+        mbar_arrive_cluster(c.bars + OFF_A_PAIR + 8 * kc, c.leader_rank);
+      }
+    }
+    mbar_wait(c.bars + OFF_MMA_DONE, g & 1u, c.wctx, code + 1);
+    if (c.leader)
+      for (uint32_t r = 0; r < (uint32_t)C_::CL; ++r) mbar_arrive_cluster(c.bars + OFF_ALL_FREE, r);
+  }
+}
+
+// Epilogue helpers ------------------------------------------------------------------------------------------------
+// "this warp has read accumulator s of step g": to the leader's barrier (remote for the odd CTA of a pair)
+template <int NP, bool PAIR>
+__device__ __forceinline__ void release_accumulator(const Ctx<NP, PAIR>& c, int s, int lane) {
+  using namespace tc;
+  tcgen05_fence_before();
+  __syncwarp();
+  if (lane == 0) {
+    if (PAIR && !c.leader) mbar_arrive_cluster(c.bars + OFF_D_EMPTY + 8 * s, c.leader_rank);
+    else mbar_arrive(c.bars + OFF_D_EMPTY + 8 * s);
+  }
+}
+
+// Writes this thread's 2 x 32 bf16 values (packed[s*16 + ..], columns [32h, 32h+32) of sub-slice s) into the CTA's own
+// two chunks of the A buffer, then (one thread) marks them complete locally and copies them to the CTAs that hold the
+// same samples for the other slices.  All 256 epilogue threads must call it.
+template <int NP, bool PAIR>
+__device__ __forceinline__ void publish_chunks(const Ctx<NP, PAIR>& c, const uint32_t* packed, int row, int h, int warp,
+                                               int lane) {
+  using C_ = Cfg<NP, PAIR>;
+  using namespace tc;
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    const uint32_t tile_addr = c.a_base + (2 * c.q + s) * CHUNK_BYTES;
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const uint32_t unit = (uint32_t)(4 * h + v);
+      const uint32_t addr = tile_addr + row * 128 + ((unit ^ ((uint32_t)row & 7u)) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[s * 16 + 4 * v]),
+                   "r"(packed[s * 16 + 4 * v + 1]), "r"(packed[s * 16 + 4 * v + 2]), "r"(packed[s * 16 + 4 * v + 3])
+                   : "memory");
+    }
+  }
+  fence_proxy_async_smem();
+  named_bar_sync(1, 256);
+  if (warp == 4 && lane == 0) {
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int kc = 2 * c.q + s;
+      const uint32_t tile_addr = c.a_base + kc * CHUNK_BYTES;
+      mbar_arrive(c.bars + OFF_A_FULL + 8 * kc);
+      for (int q2 = 0; q2 < C_::C; ++q2)
+        if (q2 != c.q) dsmem_bulk_copy(tile_addr, tile_addr, CHUNK_BYTES, c.bars + OFF_A_FULL + 8 * kc, c.peer_rank(q2));
+    }
+  }
+}
+
 }  // namespace tcr
+
+// How many clusters to launch: one per tile, but never more than can be resident at once (a second wave would
+// double the time of these persistent kernels; with fewer clusters the tiles are taken round-robin instead).
+inline int clusters_to_launch(const void* kernel, cudaLaunchConfig_t* cfg, int cluster_size, int n_tiles) {
+  int max_active = 0;
+  cfg->gridDim = dim3((unsigned)(cluster_size * n_tiles), 1, 1);
+  if (cudaOccupancyMaxActiveClusters(&max_active, kernel, cfg) != cudaSuccess || max_active < 1) {
+    (void)cudaGetLastError();
+    max_active = 148 / cluster_size;
+  }
+  if (getenv("RINGRNN_DEBUG") != nullptr)
+    fprintf(stderr, "[ringrnn] cluster size %d: %d tiles, at most %d clusters resident\n", cluster_size, n_tiles, max_active);
+  return n_tiles < max_active ? n_tiles : max_active;
+}
+
 }  // namespace ringrnn
