@@ -35,6 +35,8 @@ WORKLOADS = {
     "c2": dict(N=256, B=1024, T=256, act="relu", max_av=0.1 * math.pi, cpu_slice=(64, 32)),
     "c3": dict(N=512, B=4096, T=512, act="gelu", max_av=0.1 * math.pi, cpu_slice=(64, 16)),
     "c4": dict(N=1024, B=8192, T=2000, act="tanh", max_av=0.05 * math.pi, cpu_slice=(16, 8)),
+    # forward-only rollout with the ideal cosine weights; decoded-angle error against the integrated target
+    "c5": dict(N=120, B=65536, T=4000, act="tanh", max_av=0.1 * math.pi, cpu_slice=(1024, 200), rollout=True),
 }
 # DRAM bytes (read + write) per sample-timestep of each bf16-mode kernel at N=512, from the ncu captures summarised
 # under profiles/ (taken at T=64, B=4096; traffic is proportional to B*T).  None = no capture for that kernel/mode.
@@ -143,6 +145,103 @@ def run_reference(args, wl):
         "cpu_baseline": {"value": rate, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": rate, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def circular_error(a, b):
+    d = torch.abs(a - b) % (2 * math.pi)
+    return torch.minimum(d, 2 * math.pi - d)
+
+
+def run_rollout(args, wl):
+    """Forward-only workload: sample-timesteps/s of the rollout + decoded-angle error (mean and final step)."""
+    from rnn_train_ring_attractor_b200 import _lib
+    from rnn_train_ring_attractor_b200.build import build
+    from rnn_train_ring_attractor_b200.fused import ring_rnn_rollout
+    from rnn_train_ring_attractor_b200.inputs import benchmark_inputs
+    from rnn_train_ring_attractor_b200.ring_rnn_cuda import choose_precision
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        raise RuntimeError("the rollout workload is a single-GPU configuration")
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    build()
+    L = _lib.lib()
+    N, B, T, act = wl["N"], wl["B"], wl["T"], wl["act"]
+    prec = "bf16" if choose_precision(B, T, N, 2, _lib.ACT[act], 2, args.precision) == 1 else "fp32"
+    host = benchmark_inputs(N, B, T, seed=1000, max_av=wl["max_av"], weights="ideal")
+    pinned = {k: host[k].pin_memory() for k in ("A", "r_init")}
+    Wa, Wo, target = host["Wa"].to(dev), host["Wo"].to(dev), host["target"].to(dev)
+    resident = {k: pinned[k].to(dev) for k in pinned}
+
+    def fwd(ins):
+        return ring_rnn_rollout(ins["A"], Wa, host["J0"], host["J1"], Wo, ins["r_init"], 0.1, act, precision=prec)
+
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    for _ in range(max(1, args.warmup)):
+        decoded, _ = fwd(resident)
+    err = circular_error(decoded, target)
+    err_mean, err_final = float(err.mean()), float(err[:, -1].mean())
+    L.ringrnn_timing_reset()
+    L.ringrnn_timing_enable(1)
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = timed(lambda: fwd(resident), args.steps)
+    L.ringrnn_timing_enable(0)
+    launches = int(L.ringrnn_launch_count())
+    kern = _lib.timing_snapshot()
+
+    def e2e_step():
+        ins = {k: pinned[k].to(dev, non_blocking=True) for k in pinned}
+        d, _ = fwd(ins)
+        return float(circular_error(d[:, -1], target[:, -1]).mean())
+
+    e2e_step()
+    ms_e2e = timed(e2e_step, max(1, args.steps // 2))
+    clocks = sampler.stop()
+    peaks, peak_src = measured_peaks()
+    ms_launch = kern["fwd_recurrent"][0] / max(1, kern["fwd_recurrent"][1])
+    achieved = 6.0 * N * N * B * T / (ms_launch * 1e-3) / 1e12
+    peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
+    cpu = None
+    if not args.no_cpu_baseline:
+        from oracle import ring_oracle as orc
+        torch.set_num_threads(os.cpu_count() or 1)
+        Bs, Ts = wl["cpu_slice"]
+        c = {k: host[k][:Bs, :Ts].contiguous() if host[k].dim() > 1 and host[k].shape[0] == B else host[k]
+             for k in ("A", "r_init", "target")}
+        c["r_init"] = host["r_init"][:Bs].contiguous()
+        t0 = time.perf_counter()
+        with torch.no_grad():
+            hist = orc.ring_forward_ref(c["A"], host["Wa"], host["J0"], host["J1"], host["Wo"], c["r_init"], 0.1, act)
+        dt = time.perf_counter() - t0
+        ref_dec = orc.decode_angle(hist)
+        cpu = {"value": Bs * Ts / dt, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+               "sample": f"slice B={Bs}, T={Ts}, forward only, no_grad",
+               "decoded_vs_oracle_mean_abs_err": float(circular_error(decoded[:Bs, :Ts].cpu(), ref_dec).mean())}
+    line = {
+        "metric": "forward sample-timesteps/s", "value": B * T / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16" if prec == "bf16" else "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: N={N}, B={B}, T={T}, {act}, alpha=0.1, ideal cosine weights, "
+                               f"forward-only rollout with per-step population-vector decode, precision mode {prec}"},
+        "decoded_angle_error": {"mean_rad": err_mean, "final_step_rad": err_final},
+        "e2e": {"value": B * T / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": sum(v.numel() * 4 for v in pinned.values()), "d2h_bytes_per_step": 4},
+        "gpu_launches": launches, "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "fwd_recurrent", "achieved": achieved, "peak": peak,
+                     "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                     "peak_source": f"{peak_src} (sustained bf16 GEMM)", "ms_per_launch": ms_launch},
+        "cpu_baseline": cpu,
     }
     print(json.dumps(line), flush=True)
 
@@ -297,6 +396,8 @@ def main():
         wl["B"] = args.batch
     if args.impl == "reference":
         run_reference(args, wl)
+    elif wl.get("rollout"):
+        run_rollout(args, wl)
     else:
         run_ours(args, wl)
 

@@ -5,7 +5,8 @@
 //   weights, forward  Wf [C*2*RB, NP] bf16 (RB = 208, or 224 when CTA pairs are used, i.e. B > 128): block (q,s) rows = {Wo[i,:], Wl[i,:], Wr[i,:] for the 64 neurons i of
 //                     sub-slice s of CTA q, a row of ones, zero rows}; columns j >= N zero
 //   weights, backward Wb, same shape: rows = {Wo[:,j], Wl[:,j], Wr[:,j] for the 64 neurons j, ones, zeros}
-//   saved             Rh [T+1][BP][NP] bf16 (Rh[0] = r_init, Rh[t+1] = r_t) | Dh [T][BP][NP] bf16 = F'(re_t)
+//   saved             Rh [T+1][BP][NP] bf16 row-major (Rh[0] = r_init, Rh[t+1] = r_t; the last slot stays unwritten:
+//                     nothing reads r_T) | Dh = F'(re_t) bf16, T*BP*NP elements in 32x32 blocks | sign masks of r_t
 //   backward scratch  DL [T*BP][3*NP] bf16 = [delta | L*delta | R*delta] (A operand of the weight-gradient
 //                     GEMM) | split-K partials | dWcat [3*NP][NP] fp32
 #include <string.h>
@@ -20,7 +21,8 @@ struct TcFwdParams;
 struct TcBwdParams;
 int tc_forward_launch(int act, int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmR0, const void* params,
                       cudaStream_t s);
-int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const void* params, cudaStream_t s);
+int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmDL, const void* params,
+                       cudaStream_t s);
 __global__ void grad_j_kernel(const float* __restrict__ raw, const float* __restrict__ Wo, size_t NN, float* grad_J);
 
 namespace {
@@ -120,10 +122,13 @@ size_t bf16_fwd_workspace_bytes(const RingRnnProblem& p) {
   const Layout l = layout_of(p);
   return 1024 + l.w_bytes + l.r0_bytes + l.dec_bytes;
 }
-// SAVED: Rh[T+1] | Dh[T]
+// SAVED: Rh[T+1] row-major | Dh[T] blocked | sign masks [T][NP/32][2][BP] uint32
+size_t sign_mask_bytes(const RingRnnProblem& p, const Layout& l) {
+  return align_up((size_t)p.T * (l.NP / 32) * 2 * l.BP * 4, 1024);
+}
 size_t bf16_saved_bytes(const RingRnnProblem& p) {
   const Layout l = layout_of(p);
-  return (size_t)(2 * p.T + 1) * l.state_bytes;
+  return (size_t)(2 * p.T + 1) * l.state_bytes + sign_mask_bytes(p, l);
 }
 
 struct TcFwdParamsHost {
@@ -133,6 +138,7 @@ struct TcFwdParamsHost {
   const float* r_init;
   __nv_bfloat16* Rh;
   __nv_bfloat16* Dh;
+  uint32_t* Sg;
   float* hist;
   float* dec_part;
   const float* dec_u;
@@ -156,6 +162,8 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   float* dec_part = reinterpret_cast<float*>(w + 1024 + l.w_bytes + l.r0_bytes);
   __nv_bfloat16* Rh = train ? static_cast<__nv_bfloat16*>(a.saved) : nullptr;
   __nv_bfloat16* Dh = train ? Rh + (size_t)(p.T + 1) * l.BP * l.NP : nullptr;
+  uint32_t* Sg = train ? reinterpret_cast<uint32_t*>(static_cast<char*>(a.saved) + (size_t)(2 * p.T + 1) * l.state_bytes)
+                       : nullptr;
   if (train) R0 = Rh;  // slot 0 of the saved state doubles as the initial A operand
 
   if (a.status == nullptr) RINGRNN_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), s));
@@ -175,7 +183,9 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   CUtensorMap tmW, tmR0;
   if (!make_tmap_bf16_2d(&tmW, Wf, (uint64_t)l.C * 2 * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, 64))
     return RINGRNN_ERR_CUDA;
-  if (!make_tmap_bf16_2d(&tmR0, R0, (uint64_t)l.BP, (uint64_t)l.NP, 128, 64)) return RINGRNN_ERR_CUDA;
+  // one map serves the initial-state loads (rows [0, BP)) and, in training, the saved-state stores (rows up to T*BP)
+  if (!make_tmap_bf16_2d(&tmR0, R0, (uint64_t)(train ? p.T + 1 : 1) * l.BP, (uint64_t)l.NP, 128, 64))
+    return RINGRNN_ERR_CUDA;
 
   const bool want_dec = a.dec_x || a.dec_y || a.dec_ta;
   TcFwdParamsHost fp;
@@ -186,7 +196,7 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   fp.n_tiles = l.BP / l.tile_rows;
   fp.J0 = p.J0; fp.J1 = p.J1; fp.alpha = p.alpha;
   fp.A = p.A; fp.r_init = p.r_init;
-  fp.Rh = Rh; fp.Dh = Dh;
+  fp.Rh = Rh; fp.Dh = Dh; fp.Sg = Sg;
   fp.hist = a.bump_history;
   fp.dec_part = want_dec ? dec_part : nullptr;
   fp.dec_u = a.dec_u; fp.dec_v = a.dec_v;
@@ -258,8 +268,8 @@ struct TcBwdParamsHost {
   int B, T, N, BP, a_dim, colL, colR, n_tiles;
   float J0, J1, alpha;
   const float* A;
-  const __nv_bfloat16* Rh;
   const __nv_bfloat16* Dh;
+  const uint32_t* Sg;
   const float* grad_output;
   const float* coef_x;
   const float* coef_y;
@@ -313,14 +323,17 @@ int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   bp.colL = colL; bp.colR = colR;
   bp.n_tiles = l.BP / l.tile_rows;
   bp.J0 = p.J0; bp.J1 = p.J1; bp.alpha = p.alpha;
-  bp.A = p.A; bp.Rh = Rh; bp.Dh = Dh;
+  bp.A = p.A; bp.Dh = Dh;
+  bp.Sg = reinterpret_cast<const uint32_t*>(static_cast<const char*>(a.saved) + (size_t)(2 * p.T + 1) * l.state_bytes);
   bp.grad_output = a.grad_output;
   bp.coef_x = a.coef_x; bp.coef_y = a.coef_y; bp.coef_s = a.coef_s;
   bp.dec_u = a.dec_u; bp.dec_v = a.dec_v;
   bp.DL = DL;
   bp.grad_r_init = a.grad_r_init;
   bp.status = status;
-  int rc = tc_backward_launch(l.NP, l.pair, tmW, &bp, s);
+  CUtensorMap tmDL;
+  if (!make_tmap_bf16_2d(&tmDL, DL, (uint64_t)p.T * l.BP, (uint64_t)3 * l.NP, 128, 64)) return RINGRNN_ERR_CUDA;
+  int rc = tc_backward_launch(l.NP, l.pair, tmW, tmDL, &bp, s);
   if (rc != RINGRNN_OK) return rc;
 
   // dWcat[3NP, NP] = DL^T [3NP, T*BP] x Rh[0..T) [T*BP, NP]

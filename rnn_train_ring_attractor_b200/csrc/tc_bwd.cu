@@ -23,8 +23,8 @@ struct TcBwdParams {
   int B, T, N, BP, a_dim, colL, colR, n_tiles;
   float J0, J1, alpha;
   const float* A;               // [B,T,a_dim]
-  const __nv_bfloat16* Rh;      // [T+1][BP][NP]
-  const __nv_bfloat16* Dh;      // [T][BP][NP]
+  const __nv_bfloat16* Dh;      // F'(re_t), blocked layout (tc_recurrent.cuh)
+  const uint32_t* Sg;           // [T][NP/32][2][BP] sign masks of r_t
   const float* grad_output;     // [T,B,N] or nullptr
   const float* coef_x;          // [B,T] or nullptr
   const float* coef_y;
@@ -38,7 +38,7 @@ struct TcBwdParams {
 
 template <int NP, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
-bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const TcBwdParams p) {
+bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmDL, const TcBwdParams p) {
   using C_ = Cfg<NP, PAIR>;
   extern __shared__ uint8_t smem_raw[];
   const Ctx<NP, PAIR> c = setup_cta<NP, PAIR>(smem_raw, p.dec_u, p.dec_v, p.N, p.status);
@@ -80,7 +80,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const TcBwdParams p) {
       for (int j = 0; j < 64; ++j) master[j] = 0.f;
       float L = 0.f, R = 0.f;        // action scalars of the step whose delta is in flight
       float Ln = 0.f, Rn = 0.f, cx = 0.f, cy = 0.f, cs = 0.f;  // prefetched for the next `produce`
-      uint4 dv[8], rv[8];            // prefetched rows of F'(re_t) and r_t (bf16): [s*4 + v]
+      uint4 dv[8];                   // prefetched F'(re_t) (bf16): [s*4 + v]
+      uint32_t mpos[2], mneg[2];     // prefetched sign masks of r_t per sub-slice
 
       // loads for produce(t); issued before the wait on the accumulators so that their latency is hidden
       auto prefetch = [&](int t) {
@@ -97,12 +98,14 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const TcBwdParams p) {
         }
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
-          const uint4* dsrc = reinterpret_cast<const uint4*>(p.Dh + ((size_t)t * p.BP + b) * NP + nq + 64 * s);
-          const uint4* rsrc = reinterpret_cast<const uint4*>(p.Rh + ((size_t)(t + 1) * p.BP + b) * NP + nq + 64 * s);
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            dv[s * 4 + v] = __ldg(dsrc + v);
-            rv[s * 4 + v] = has_coef ? __ldg(rsrc + v) : make_uint4(0u, 0u, 0u, 0u);
+          const int n32 = (nq + 64 * s) >> 5;
+          load_blocked(p.Dh + blocked_offset(t, b, n32, p.BP, NP), lane, dv + 4 * s);
+          mpos[s] = 0u;
+          mneg[s] = 0u;
+          if (has_coef) {
+            const uint32_t* sg = p.Sg + (((size_t)t * (NP >> 5) + n32) * 2) * p.BP + b;
+            mpos[s] = __ldg(sg);
+            mneg[s] = __ldg(sg + p.BP);
           }
         }
       };
@@ -136,7 +139,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const TcBwdParams p) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             const uint32_t dw[4] = {dv[s * 4 + v].x, dv[s * 4 + v].y, dv[s * 4 + v].z, dv[s * 4 + v].w};
-            const uint32_t rw[4] = {rv[s * 4 + v].x, rv[s * 4 + v].y, rv[s * 4 + v].z, rv[s * 4 + v].w};
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
               float dl[2];
@@ -146,8 +148,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const TcBwdParams p) {
                 const int idx = s * 32 + j;
                 float gg = master[idx];
                 if (has_coef) {
-                  const float rr = e ? bf16_hi(rw[w]) : bf16_lo(rw[w]);
-                  const float sg = (rr > 0.f) ? 1.f : ((rr < 0.f) ? -1.f : 0.f);
+                  const float sg = (float)((mpos[s] >> j) & 1u) - (float)((mneg[s] >> j) & 1u);
                   gg = fmaf(cx, uv[64 * s + 32 * h + j], gg);
                   gg = fmaf(cy, uv[128 + 64 * s + 32 * h + j], gg);
                   gg = fmaf(cs, sg, gg);
@@ -160,27 +161,30 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const TcBwdParams p) {
             }
           }
         }
-        publish_chunks<NP, PAIR>(c, packed, row, h, warp, lane);
+        // delta_t: A operand of this step everywhere, and column block 0 of DL row block t (TMA store from the chunks)
+        publish_chunks<NP, PAIR>(c, packed, row, h, warp, lane, &tmDL, q * 128,
+                                 t * p.BP + tile * C_::TILE_ROWS + c.half * 128);
+        if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 12);
         // off the critical path: [delta | L*delta | R*delta] for the weight-gradient GEMM.  The scaled copies are
         // formed from the bf16 delta the MMA sees, so the three blocks are consistent with one another.
+        const uint32_t stage = c.stage_base + (uint32_t)(warp - 4) * 2048u;
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
-          __nv_bfloat16* drow = p.DL + ((size_t)t * p.BP + b) * (3 * NP) + nq + 64 * s;
+          // row 0 of this warp's 32-row block, first of this thread's 32 columns, column block 0
+          uint8_t* blk0 = reinterpret_cast<uint8_t*>(p.DL + ((size_t)t * p.BP + (b - lane)) * (3 * NP) + nq + 64 * s);
+          uint32_t o[16];
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint32_t o1[4], o2[4];
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-              const uint32_t d2 = packed[s * 16 + v * 4 + w];
-              const float lo = bf16_lo(d2), hi = bf16_hi(d2);
-              o1[w] = pack_bf16x2(L * lo, L * hi);
-              o2[w] = pack_bf16x2(R * lo, R * hi);
-            }
-            *reinterpret_cast<uint4*>(drow + v * 8) = make_uint4(packed[s * 16 + v * 4], packed[s * 16 + v * 4 + 1],
-                                                                  packed[s * 16 + v * 4 + 2], packed[s * 16 + v * 4 + 3]);
-            *reinterpret_cast<uint4*>(drow + NP + v * 8) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
-            *reinterpret_cast<uint4*>(drow + 2 * NP + v * 8) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+          for (int w = 0; w < 16; ++w) {
+            const uint32_t d2 = packed[s * 16 + w];
+            o[w] = pack_bf16x2(L * bf16_lo(d2), L * bf16_hi(d2));
           }
+          store_rows_via_smem(stage, lane, o, blk0 + (size_t)NP * 2, (size_t)3 * NP * 2);
+#pragma unroll
+          for (int w = 0; w < 16; ++w) {
+            const uint32_t d2 = packed[s * 16 + w];
+            o[w] = pack_bf16x2(R * bf16_lo(d2), R * bf16_hi(d2));
+          }
+          store_rows_via_smem(stage, lane, o, blk0 + (size_t)2 * NP * 2, (size_t)3 * NP * 2);
         }
       };
 
@@ -192,6 +196,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const TcBwdParams p) {
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
           mbar_wait(bars + OFF_D_FULL + 8 * s, g & 1u, wctx, 307);
+          if (warp == 4 && lane == 0) RINGRNN_STAMP(g, s == 0 ? 5 : 7);
           tcgen05_fence_after();
           if (s == 0) {
             uint32_t sraw;
@@ -218,10 +223,14 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const TcBwdParams p) {
             }
           }
           release_accumulator<NP, PAIR>(c, s, lane);
+          if (warp == 4 && lane == 0) RINGRNN_STAMP(g, s == 0 ? 6 : 8);
         }
+        if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 9);
         mbar_wait<true>(bars + OFF_ALL_FREE, g & 1u, wctx, 308);
+        if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 10);
         if (t > 0) {
           produce(t - 1);
+          if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 11);
         } else if (p.grad_r_init != nullptr && valid) {
 #pragma unroll
           for (int s = 0; s < 2; ++s)
@@ -231,12 +240,13 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const TcBwdParams p) {
         }
       }
     }
+    if (warp == 4 && lane == 0) bulk_wait_all<0>();  // the delta stores have left shared memory and landed
   }
   teardown_cta<NP, PAIR>(c);
 }
 
 template <int NP, bool PAIR>
-static int launch_bwd_tc(const CUtensorMap& tmW, const TcBwdParams& p, cudaStream_t s) {
+static int launch_bwd_tc(const CUtensorMap& tmW, const CUtensorMap& tmDL, const TcBwdParams& p, cudaStream_t s) {
   using C_ = Cfg<NP, PAIR>;
   auto kernel = bwd_tc_kernel<NP, PAIR>;
   RINGRNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM));
@@ -256,17 +266,24 @@ static int launch_bwd_tc(const CUtensorMap& tmW, const TcBwdParams& p, cudaStrea
   cfg.gridDim = dim3(n_clusters * C_::CL, 1, 1);
   {
     LaunchScope ls(K_BWD, s);
-    RINGRNN_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmW, p));
+    RINGRNN_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmW, tmDL, p));
   }
   return RINGRNN_OK;
 }
 
-int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const void* params, cudaStream_t s) {
+int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmDL, const void* params,
+                       cudaStream_t s) {
   const TcBwdParams& p = *static_cast<const TcBwdParams*>(params);  // same field order as the host-side mirror
-  if (NP == 128) return pair ? launch_bwd_tc<128, true>(tmW, p, s) : launch_bwd_tc<128, false>(tmW, p, s);
-  if (NP == 256) return pair ? launch_bwd_tc<256, true>(tmW, p, s) : launch_bwd_tc<256, false>(tmW, p, s);
-  if (NP == 512) return pair ? launch_bwd_tc<512, true>(tmW, p, s) : launch_bwd_tc<512, false>(tmW, p, s);
+  if (NP == 128) return pair ? launch_bwd_tc<128, true>(tmW, tmDL, p, s) : launch_bwd_tc<128, false>(tmW, tmDL, p, s);
+  if (NP == 256) return pair ? launch_bwd_tc<256, true>(tmW, tmDL, p, s) : launch_bwd_tc<256, false>(tmW, tmDL, p, s);
+  if (NP == 512) return pair ? launch_bwd_tc<512, true>(tmW, tmDL, p, s) : launch_bwd_tc<512, false>(tmW, tmDL, p, s);
   return RINGRNN_ERR_UNSUPPORTED;
 }
 
 }  // namespace ringrnn
+
+#ifdef RINGRNN_TIMELINE
+extern "C" int ringrnn_debug_timeline_read_bwd(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, ringrnn::g_timeline, sizeof(long long) * 64 * 16);
+}
+#endif

@@ -23,7 +23,8 @@ struct TcFwdParams {
   const float* A;        // [B,T,a_dim]
   const float* r_init;   // [B,N]
   __nv_bfloat16* Rh;     // [T+1][BP][NP] (slot 0 = bf16(r_init), prepared before launch) or nullptr
-  __nv_bfloat16* Dh;     // [T][BP][NP] or nullptr
+  __nv_bfloat16* Dh;     // F'(re_t), blocked layout (tc_recurrent.cuh), T*BP*NP elements, or nullptr
+  uint32_t* Sg;          // [T][NP/32][2][BP] bit masks of r_t > 0 and r_t < 0 (bit j = neuron 32*block + j), or nullptr
   float* hist;           // [T,B,N] or nullptr
   float* dec_part;       // [2C][3][T][BP] or nullptr
   const float* dec_u;    // [N]
@@ -125,7 +126,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           }
           release_accumulator<NP, PAIR>(c, s, lane);  // the accumulator is in registers: hand it back
           if (warp == 4 && lane == 0) RINGRNN_STAMP(g, s == 0 ? 6 : 8);
-          uint32_t dpk[16];
+          uint32_t dpk[16], pos = 0u, neg = 0u;
 #pragma unroll
           for (int j0 = 0; j0 < 32; j0 += 8) {
             float re[8], f[8], d[8];
@@ -143,6 +144,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               if (nq + 64 * s + j0 + e >= p.N) { r = 0.f; d[e] = 0.f; }
               master[idx] = r;
               f[e] = r;
+              pos |= (r > 0.f ? 1u : 0u) << (j0 + e);
+              neg |= (r < 0.f ? 1u : 0u) << (j0 + e);
               if (want_dec) {
                 px = fmaf(r, uv[64 * s + 32 * h + j0 + e], px);
                 py = fmaf(r, uv[128 + 64 * s + 32 * h + j0 + e], py);
@@ -156,9 +159,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             }
           }
           if (p.Dh != nullptr) {
-            uint4* dst = reinterpret_cast<uint4*>(p.Dh + ((size_t)t * p.BP + b) * NP + nq + 64 * s);
-#pragma unroll
-            for (int v = 0; v < 4; ++v) dst[v] = make_uint4(dpk[4 * v], dpk[4 * v + 1], dpk[4 * v + 2], dpk[4 * v + 3]);
+            const int n32 = (nq + 64 * s) >> 5;
+            store_blocked(p.Dh + blocked_offset(t, b, n32, p.BP, NP), lane, dpk);
+            uint32_t* sg = p.Sg + (((size_t)t * (NP >> 5) + n32) * 2) * p.BP + b;
+            sg[0] = pos;
+            sg[p.BP] = neg;
           }
         }
         // every CTA of the cluster has finished reading r_{t-1} (waited for in every step so that no phase of
@@ -166,19 +171,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 9);
         mbar_wait<true>(bars + OFF_ALL_FREE, g & 1u, wctx, 208);
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 10);
-        if (t + 1 < T) publish_chunks<NP, PAIR>(c, packed, row, h, warp, lane);
+        // r_t becomes the A operand of step t+1 everywhere and, in training, row block t+1 of the saved state
+        if (t + 1 < T)
+          publish_chunks<NP, PAIR>(c, packed, row, h, warp, lane, p.Rh != nullptr ? &tmR0 : nullptr, q * 128,
+                                   (t + 1) * p.BP + tile * C_::TILE_ROWS + c.half * 128);
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 11);
-        // off the critical path: saved state, fp32 history, decode sums
-        if (p.Rh != nullptr) {
-#pragma unroll
-          for (int s = 0; s < 2; ++s) {
-            uint4* dst = reinterpret_cast<uint4*>(p.Rh + ((size_t)(t + 1) * p.BP + b) * NP + nq + 64 * s);
-#pragma unroll
-            for (int v = 0; v < 4; ++v)
-              dst[v] = make_uint4(packed[s * 16 + 4 * v], packed[s * 16 + 4 * v + 1], packed[s * 16 + 4 * v + 2],
-                                  packed[s * 16 + 4 * v + 3]);
-          }
-        }
+        // off the critical path: fp32 history, decode sums
         if (p.hist != nullptr && valid) {
 #pragma unroll
           for (int s = 0; s < 2; ++s) {
@@ -211,6 +209,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             if (nq + 64 * s + j < p.N) p.final_state[(size_t)b * p.N + nq + 64 * s + j] = master[s * 32 + j];
       }
     }
+    if (warp == 4 && lane == 0) bulk_wait_all<0>();  // the saved-state stores have left shared memory and landed
   }
   teardown_cta<NP, PAIR>(c);
 }

@@ -75,10 +75,11 @@ struct Cfg {
   static constexpr int A_BYTES = KC * CHUNK_BYTES;
   static constexpr int TILES = 2 * KC;           // weight tiles per step
   static constexpr int AUX = 2048;               // barriers, flags, decode vectors
-  static constexpr int NS_FIT = (SMEM_LIMIT - 1024 - AUX - A_BYTES) / WT_BYTES;
+  static constexpr int STAGE_BYTES = 8 * 2048;   // one 32-row x 64-byte transposition buffer per epilogue warp
+  static constexpr int NS_FIT = (SMEM_LIMIT - 1024 - AUX - STAGE_BYTES - A_BYTES) / WT_BYTES;
   static constexpr bool RESIDENT = NS_FIT >= TILES;
   static constexpr int NS = RESIDENT ? TILES : (NS_FIT > 16 ? 16 : NS_FIT);
-  static constexpr int SMEM = 1024 + A_BYTES + NS * WT_BYTES + AUX;
+  static constexpr int SMEM = 1024 + A_BYTES + NS * WT_BYTES + AUX + STAGE_BYTES;
   static_assert(NS >= 2, "weight ring too small");
   static_assert(NS <= 16, "barrier block sized for 16 stages");
   static_assert(WT_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
@@ -172,7 +173,7 @@ __device__ __forceinline__ void act_group(const float* x, float* f, float* d) {
 // ---- per-CTA context and the roles both directions share -------------------------------------------------------
 template <int NP, bool PAIR>
 struct Ctx {
-  uint32_t a_base, w_base, bars, tmem_base;
+  uint32_t a_base, w_base, bars, tmem_base, stage_base;
   int q;            // neuron slice of this CTA
   int half;         // which 128 of the tile's samples (always 0 in the single shape)
   bool leader;      // issues the MMAs (every CTA in the single shape, the even CTA of a pair otherwise)
@@ -195,6 +196,7 @@ __device__ __forceinline__ Ctx<NP, PAIR> setup_cta(uint8_t* smem_raw, const floa
   c.a_base = base;
   c.w_base = base + C_::A_BYTES;
   c.bars = c.w_base + C_::NS * C_::WT_BYTES;
+  c.stage_base = c.bars + C_::AUX;
   uint8_t* bars_gen = gen + C_::A_BYTES + C_::NS * C_::WT_BYTES;
   volatile uint32_t* tmem_slot_p = reinterpret_cast<volatile uint32_t*>(bars_gen + OFF_TMEM_SLOT);
   volatile int* dead = reinterpret_cast<volatile int*>(bars_gen + OFF_DEAD);
@@ -270,12 +272,13 @@ __device__ __forceinline__ void producer_loop(const Ctx<NP, PAIR>& c, const CUte
   constexpr int KC = C_::KC, NS = C_::NS;
   tma_prefetch_desc(tmW);
   if (total_steps == 0) return;
+  const uint64_t keep = l2_policy_evict_last();
   auto issue = [&](int st, int s, int kc) {
     const uint32_t bar = c.bars + OFF_W_FULL + 8 * st;
     const int y = (c.q * 2 + s) * C_::RB + c.half * C_::WROWS;
     if (c.leader) mbar_arrive_expect_tx(bar, (PAIR ? 2 : 1) * C_::WT_BYTES);  // a pair's two halves land on one barrier
     if (PAIR) tma_load_2d_pair(c.w_base + st * C_::WT_BYTES, tmW, bar, kc * 64, y);
-    else tma_load_2d(c.w_base + st * C_::WT_BYTES, tmW, bar, kc * 64, y);
+    else tma_load_2d_hint(c.w_base + st * C_::WT_BYTES, tmW, bar, kc * 64, y, keep);
   };
   if (C_::RESIDENT) {
     for (int s = 0; s < 2; ++s)
@@ -424,13 +427,21 @@ __device__ __forceinline__ void release_accumulator(const Ctx<NP, PAIR>& c, int 
 }
 
 // Writes this thread's 2 x 32 bf16 values (packed[s*16 + ..], columns [32h, 32h+32) of sub-slice s) into the CTA's own
-// two chunks of the A buffer, then (one thread) marks them complete locally and copies them to the CTAs that hold the
-// same samples for the other slices.  All 256 epilogue threads must call it.
+// two chunks of the A buffer, then (one thread) marks them complete locally, copies them to the CTAs that hold the
+// same samples for the other slices and, if `tm_store` is given, stores them with TMA to rows [y, y+128),
+// columns [x0, x0+128) of a row-major bf16 tensor (the saved state, or delta for the weight-gradient GEMM): the
+// chunks are already in the layout a 128-byte-swizzled TMA box expects, so this costs no load/store instructions.
+// All 256 epilogue threads must call it.
 template <int NP, bool PAIR>
 __device__ __forceinline__ void publish_chunks(const Ctx<NP, PAIR>& c, const uint32_t* packed, int row, int h, int warp,
-                                               int lane) {
+                                               int lane, const CUtensorMap* tm_store, int x0, int y) {
   using C_ = Cfg<NP, PAIR>;
   using namespace tc;
+  // the TMA stores of the previous call have finished reading the chunks (the issuing thread waits before arriving)
+  if (tm_store != nullptr) {
+    if (warp == 4 && lane == 0) bulk_wait_read<0>();
+    named_bar_sync(2, 256);
+  }
 #pragma unroll
   for (int s = 0; s < 2; ++s) {
     const uint32_t tile_addr = c.a_base + (2 * c.q + s) * CHUNK_BYTES;
@@ -454,7 +465,59 @@ __device__ __forceinline__ void publish_chunks(const Ctx<NP, PAIR>& c, const uin
       for (int q2 = 0; q2 < C_::C; ++q2)
         if (q2 != c.q) dsmem_bulk_copy(tile_addr, tile_addr, CHUNK_BYTES, c.bars + OFF_A_FULL + 8 * kc, c.peer_rank(q2));
     }
+    if (tm_store != nullptr) {
+#pragma unroll
+      for (int s = 0; s < 2; ++s) tma_store_2d(tm_store, c.a_base + (2 * c.q + s) * CHUNK_BYTES, x0 + 64 * s, y);
+      bulk_commit();
+    }
   }
+}
+
+// ---- epilogue global-memory traffic ---------------------------------------------------------------------------
+// A thread owns one sample (row) and 32 consecutive neurons: 64 bytes of a bf16 row.  Writing or reading that
+// directly makes every warp instruction touch 32 different cache lines.  Two remedies:
+//  * tensors only these kernels read (the activation-derivative history) live in a BLOCKED layout: one 2 KB block per
+//    (32 samples, 32 neurons), 16-byte piece v of sample r at byte v*512 + r*16, so a warp instruction is one
+//    contiguous 512 bytes;
+//  * row-major tensors the GEMM reads by TMA go through a per-warp 2 KB transposition buffer in shared memory, after
+//    which each warp instruction covers 8 rows x 64 bytes.
+__device__ __forceinline__ size_t blocked_offset(int t, int b, int n32, int BP, int NP) {
+  // element offset of the block that holds sample b, neurons [32*n32, 32*n32+32) at step t
+  return (((size_t)t * (BP >> 5) + (b >> 5)) * (NP >> 5) + n32) * 1024;
+}
+__device__ __forceinline__ void store_blocked(__nv_bfloat16* base, int lane, const uint32_t* w16) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v)
+    tc::st_cs_v4(reinterpret_cast<uint8_t*>(base) + v * 512 + lane * 16, w16[4 * v], w16[4 * v + 1], w16[4 * v + 2],
+                 w16[4 * v + 3]);
+}
+__device__ __forceinline__ void load_blocked(const __nv_bfloat16* base, int lane, uint4* out4) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v) out4[v] = tc::ld_cs_v4(reinterpret_cast<const uint8_t*>(base) + v * 512 + lane * 16);
+}
+// The warp's 32 rows x 64 bytes (lane = row, w16 = its 16 words) to row-major global memory: `dst_row0` points at
+// row 0 of the warp's block, consecutive rows are `row_stride_bytes` apart; `stage` is the warp's 2 KB buffer.
+__device__ __forceinline__ void store_rows_via_smem(uint32_t stage, int lane, const uint32_t* w16, uint8_t* dst_row0,
+                                                    size_t row_stride_bytes) {
+  const uint32_t sw = ((uint32_t)lane >> 1) & 3u;
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const uint32_t addr = stage + lane * 64 + (((uint32_t)v ^ sw) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w16[4 * v]), "r"(w16[4 * v + 1]),
+                 "r"(w16[4 * v + 2]), "r"(w16[4 * v + 3])
+                 : "memory");
+  }
+  __syncwarp();
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int r = 8 * k + (lane >> 2);
+    const uint32_t piece = (uint32_t)lane & 3u;
+    const uint32_t addr = stage + r * 64 + ((piece ^ (((uint32_t)r >> 1) & 3u)) << 4);
+    uint32_t a, b, c2, d;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c2), "=r"(d) : "r"(addr));
+    tc::st_cs_v4(dst_row0 + (size_t)r * row_stride_bytes + piece * 16, a, b, c2, d);
+  }
+  __syncwarp();
 }
 
 }  // namespace tcr
