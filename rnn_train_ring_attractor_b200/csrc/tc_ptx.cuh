@@ -273,6 +273,14 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       : "memory");
 }
 
+// Completion of this CTA's MMAs issued so far, signalled on the barrier at this shared-memory offset in every CTA
+// of `cta_mask` (bit i = cluster rank i): an mbarrier arrive fanned out by the hardware, not a data copy.
+__device__ __forceinline__ void umma_commit_fanout(uint32_t bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(cta_mask)
+               : "memory");
+}
+
 // 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives lane (base_lane + i)
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile(

@@ -375,6 +375,10 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
       RINGRNN_STAMP(g, s == 0 ? 3 : 4);
     }
     commit(c.bars + OFF_MMA_DONE);
+    // "this MMA unit no longer reads the A buffers of step g", straight to every CTA of the cluster
+    if (PAIR) umma_commit_pair(c.bars + OFF_ALL_FREE, (uint16_t)((1u << C_::CL) - 1u));
+    else if (C_::CL > 1) umma_commit_fanout(c.bars + OFF_ALL_FREE, (uint16_t)((1u << C_::CL) - 1u));
+    else umma_commit(c.bars + OFF_ALL_FREE);
 #ifdef RINGRNN_TIMELINE
     RINGRNN_STAMP_VAL(g, 13, acc_w);
     RINGRNN_STAMP_VAL(g, 14, acc_a);
@@ -383,10 +387,10 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
   }
 }
 
-// Relay (one thread per CTA): follows every phase of mma_done.  The leader then tells every CTA of the cluster that
-// its MMA unit no longer reads the A buffers of step g; the odd CTA of a pair forwards "chunk kc is complete here"
-// to its leader and arms its own incoming copies.  `tile_start(tile_index)` runs before the first step of each tile
-// (forward: TMA load of the initial state into this CTA's A buffer).
+// Relay (one thread per CTA): follows every phase of mma_done, so it knows when the A buffer may take the next tile:
+// `tile_start(tile_index)` runs before the first step of each tile (forward: TMA load of the initial state into this
+// CTA's A buffer).  The odd CTA of a pair also forwards "chunk kc is complete here" to its leader and arms its own
+// incoming copies.
 template <int NP, bool PAIR, bool FWD, class TileStart>
 __device__ __forceinline__ void relay_loop(const Ctx<NP, PAIR>& c, uint32_t total_steps, int T, int code,
                                            TileStart tile_start) {
@@ -408,8 +412,6 @@ __device__ __forceinline__ void relay_loop(const Ctx<NP, PAIR>& c, uint32_t tota
       }
     }
     mbar_wait(c.bars + OFF_MMA_DONE, g & 1u, c.wctx, code + 1);
-    if (c.leader)
-      for (uint32_t r = 0; r < (uint32_t)C_::CL; ++r) mbar_arrive_cluster(c.bars + OFF_ALL_FREE, r);
   }
 }
 
