@@ -41,8 +41,8 @@ WORKLOADS = {
 # DRAM bytes (read + write) per sample-timestep of each bf16-mode kernel at N=512, from the ncu captures summarised
 # under profiles/ (taken at T=64, B=4096; traffic is proportional to B*T).  None = no capture for that kernel/mode.
 NCU_DRAM_BYTES_PER_SAMPLE_STEP = {
-    ("bf16", 512): {"fwd_recurrent": (16.67e6 + 516.53e6) / (4096 * 64), "bwd_recurrent": (551.35e6 + 761.25e6) / (4096 * 64),
-                    "dw_product": (1074.6e6 + 3.94e6) / (4096 * 64)},
+    ("bf16", 512): {"fwd_recurrent": (16.50e6 + 544.22e6) / (4096 * 64), "bwd_recurrent": (309.06e6 + 750.17e6) / (4096 * 64),
+                    "dw_product": (1074.0e6 + 3.95e6) / (4096 * 64)},
 }
 METRIC = "fwd+bwd sample-timesteps/s"
 UNIT = "sample-timesteps/s"
