@@ -320,13 +320,15 @@ def make_case(N, B, T, act, seed=0, alpha=0.1, max_av=0.1 * math.pi, weights="ra
                     J0=-0.1, J1=0.1, alpha=alpha, act=act)
 
 
-def train_step_ref(case: RingCase, lean=False, bump_weight=0.2):
-    """One fwd + loss + bwd of the reference PyTorch path on CPU.  Returns (loss, dWo, dWa, hist)."""
-    Wa = case.Wa.clone().requires_grad_(True)
-    Wo = case.Wo.clone().requires_grad_(True)
+def train_step_ref(case: RingCase, lean=False, bump_weight=0.2, dtype=None):
+    """One fwd + loss + bwd of the reference PyTorch path on CPU.  Returns (loss, dWo, dWa, hist).
+    `dtype=torch.float64` evaluates the same step in double precision (the arbiter when two fp32 evaluations differ)."""
+    cast = (lambda t: t.to(dtype)) if dtype is not None else (lambda t: t)
+    Wa = cast(case.Wa).clone().requires_grad_(True)
+    Wo = cast(case.Wo).clone().requires_grad_(True)
     fwd = ring_forward_lean if lean else ring_forward_ref
-    hist = fwd(case.A, Wa, case.J0, case.J1, Wo, case.r_init, case.alpha, case.act)
-    loss = training_loss_ref(hist, case.target, bump_weight)
+    hist = fwd(cast(case.A), Wa, case.J0, case.J1, Wo, cast(case.r_init), case.alpha, case.act)
+    loss = training_loss_ref(hist, cast(case.target), bump_weight)
     loss.backward()
     return loss.detach(), Wo.grad, Wa.grad, hist.detach()
 

@@ -133,3 +133,18 @@ def timing_snapshot():
         check(L.ringrnn_timing_read(slot, C.byref(ms), C.byref(n)))
         out[L.ringrnn_timing_name(slot).decode()] = (ms.value, n.value)
     return out
+
+
+CHECK_DEVICE_STATUS = os.environ.get("RINGRNN_CHECK", "0") == "1"
+
+
+def check_device_status(workspace, what):
+    """With RINGRNN_CHECK=1: synchronise and raise if a bf16-mode kernel abandoned a bounded wait (the first word of
+    its scratch buffer is the status word).  Off by default because it costs a device synchronisation per call."""
+    if not CHECK_DEVICE_STATUS:
+        return
+    import torch
+    torch.cuda.synchronize()
+    code = int(workspace[:4].view(torch.int32)[0])
+    if code != 0:
+        raise RingRnnError(6, f"{what}: a bounded device-side wait ran out (code {code})")

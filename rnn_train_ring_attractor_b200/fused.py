@@ -75,6 +75,8 @@ class RingRnnFusedFunc(Function):
             a.final_state = final_state.data_ptr()
             a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
             _lib.check(L.ringrnn_fwd(C.byref(a), stream))
+            if prec == _lib.PREC["bf16"]:
+                _lib.check_device_status(ws, "forward")
             red = torch.empty(2 * B, device=dev, dtype=torch.float32)
             _lib.check(L.ringrnn_angle_loss(B, T, scal[0].data_ptr(), scal[1].data_ptr(), scal[2].data_ptr(),
                                             target.data_ptr(), float(bump_weight), float(inv_count),
@@ -122,6 +124,8 @@ class RingRnnFusedFunc(Function):
             a.grad_r_init = None if grad_r is None else grad_r.data_ptr()
             a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
             _lib.check(L.ringrnn_bwd(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+            if ctx.prec == _lib.PREC["bf16"]:
+                _lib.check_device_status(ws, "backward")
             if ctx.grad_buffer is not None:
                 ctx.grad_buffer[:(1 + a_dim) * N * N + 2].mul_(g_loss)
             else:

@@ -136,6 +136,8 @@ class RingRnnCudaFunc(Function):
             a.saved, a.saved_bytes = saved.data_ptr(), saved.numel()
             a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
             _lib.check(L.ringrnn_fwd(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+            if prec == _lib.PREC["bf16"]:
+                _lib.check_device_status(ws, "forward")
         ctx.save_for_backward(action_signal, Wa, Wo, bump_history, r_init, saved)
         ctx.J0 = J0
         ctx.J1 = J1
@@ -175,6 +177,8 @@ class RingRnnCudaFunc(Function):
             a.grad_r_init = None if grad_r is None else grad_r.data_ptr()
             a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
             _lib.check(L.ringrnn_bwd(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+            if ctx.prec == _lib.PREC["bf16"]:
+                _lib.check_device_status(ws, "backward")
         gJ0 = grad_J[0].reshape(ctx.J0.shape) if (torch.is_tensor(ctx.J0) and ctx.J0.requires_grad) else None
         gJ1 = grad_J[1].reshape(ctx.J1.shape) if (torch.is_tensor(ctx.J1) and ctx.J1.requires_grad) else None
         return None, grad_Wa, gJ0, gJ1, grad_Wo, grad_r, None, None
