@@ -77,7 +77,9 @@ def generator_case(m_data, name, B, T, seed, max_av):
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference")
+    ref = sys.argv[1]
     m_nogain, m_ring, m_data = import_reference(ref)
     model_case(m_nogain, m_ring, m_data, "ref_tanh_n24", 24, 5, 12, "tanh", 2, 1)
     model_case(m_nogain, m_ring, m_data, "ref_relu_n40", 40, 6, 9, "relu", 2, 2)
