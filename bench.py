@@ -321,12 +321,36 @@ def run_ours(args, wl):
     # ---- end to end: pinned host inputs -> loss on the host ------------------------------------------
     h2d = sum(pinned[k].numel() * 4 for k in pinned)
 
+    # Double-buffered: while step i computes, a copy stream brings step i+1's inputs from pinned host memory, as a
+    # training loop would.  Every step still pays one H2D copy of (A, r_init, target) and one D2H read of the loss.
+    keys = ("A", "r_init", "target")
+    copy_stream = torch.cuda.Stream(device=dev)
+    bufs = [{k: torch.empty_like(pinned[k], device=dev) for k in keys} for _ in range(2)]
+    ready = [torch.cuda.Event(), torch.cuda.Event()]
+    free = [torch.cuda.Event(), torch.cuda.Event()]
+    for ev in free:
+        ev.record()
+    counter = {"i": 0}
+
+    def issue_copy(slot):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(free[slot])
+            for k in keys:
+                bufs[slot][k].copy_(pinned[k], non_blocking=True)
+            ready[slot].record(copy_stream)
+
+    issue_copy(0)
+
     def e2e_step():
-        ins = tuple(pinned[k].to(dev, non_blocking=True) for k in ("A", "r_init", "target"))
-        l, _ = step(ins)
+        slot = counter["i"] & 1
+        issue_copy(slot ^ 1)
+        torch.cuda.current_stream().wait_event(ready[slot])
+        l, _ = step(tuple(bufs[slot][k] for k in keys))
+        free[slot].record()
+        counter["i"] += 1
         return float(l)  # device -> host read of the step's result
 
-    for _ in range(max(1, args.warmup // 2)):
+    for _ in range(max(2, args.warmup // 2)):
         e2e_step()
     ms_e2e = timed(e2e_step, args.steps)
     clocks = sampler.stop()
@@ -368,7 +392,9 @@ def run_ours(args, wl):
                    "global_batch": B_global, "parallelism": f"dp{world}",
                    "l2": "working set (saved states + delta, several GB) exceeds the 126 MB L2; no flush needed"},
         "e2e": {"value": B_global * T / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                "how": "public API ring_rnn_fused via dp.train_step; inputs in pinned host memory, H2D double-buffered on a "
+                       "copy stream, loss read back every step"},
         "gpu_launches": launches, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "loss": loss_value,
     }
     print(json.dumps(line), flush=True)

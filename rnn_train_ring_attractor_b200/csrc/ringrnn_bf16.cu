@@ -23,7 +23,6 @@ int tc_forward_launch(int act, int NP, bool pair, const CUtensorMap& tmW, const 
                       cudaStream_t s);
 int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmDL, const void* params,
                        cudaStream_t s);
-__global__ void grad_j_kernel(const float* __restrict__ raw, const float* __restrict__ Wo, size_t NN, float* grad_J);
 
 namespace {
 
@@ -347,9 +346,9 @@ int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   }
   RINGRNN_CUDA_TRY(cudaGetLastError());
   if (a.grad_J != nullptr) {
-    LaunchScope ls(K_REDUCE, s);
-    grad_j_kernel<<<1, 1024, 0, s>>>(raw, p.Wo, NN, a.grad_J);
-    RINGRNN_CUDA_TRY(cudaGetLastError());
+    // the split-K partials are dead after the reduction inside tc_gemm: their storage serves as scratch
+    rc = launch_grad_j(raw, p.Wo, NN, a.grad_J, reinterpret_cast<double*>(partial), s);
+    if (rc != RINGRNN_OK) return rc;
   }
   return RINGRNN_OK;
 }

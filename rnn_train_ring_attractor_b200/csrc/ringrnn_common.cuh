@@ -83,6 +83,10 @@ struct DevProblem {
   int cols[RINGRNN_MAX_ACTIVE];  // active action columns
 };
 
+// dJ0 / dJ1 from the unscaled Wo gradient (ringrnn_fp32.cu); scratch: GRAD_J_BLOCKS * 2 doubles
+constexpr int GRAD_J_BLOCKS = 128;
+int launch_grad_j(const float* raw, const float* Wo, size_t NN, float* grad_J, double* scratch, cudaStream_t s);
+
 // fp32 (CUDA-core) path ----------------------------------------------------------------------
 size_t fp32_fwd_workspace_bytes(const RingRnnProblem& p);
 size_t fp32_saved_bytes(const RingRnnProblem& p, int history_given);

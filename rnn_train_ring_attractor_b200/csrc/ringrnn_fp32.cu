@@ -372,11 +372,13 @@ __global__ void dw_reduce_kernel(DevProblem p, const float* __restrict__ partial
 
 }  // namespace
 
-// dJ0 = sum_ij G_ij, dJ1 = sum_ij G_ij Wo_ij with G = sum_{t,b} delta^T r_prev (one block, fixed order)
-__global__ void grad_j_kernel(const float* __restrict__ raw, const float* __restrict__ Wo, size_t NN, float* grad_J) {
-  __shared__ double s0[1024], s1[1024];
+// dJ0 = sum_ij G_ij, dJ1 = sum_ij G_ij Wo_ij with G = sum_{t,b} delta^T r_prev.  Two passes, fixed order: `partial`
+// holds 2 doubles per block of the first pass (grid GRAD_J_BLOCKS), the second pass (one block) adds them up.
+__global__ void grad_j_partial_kernel(const float* __restrict__ raw, const float* __restrict__ Wo, size_t NN,
+                                      double* __restrict__ partial) {
+  __shared__ double s0[256], s1[256];
   double a0 = 0.0, a1 = 0.0;
-  for (size_t e = threadIdx.x; e < NN; e += blockDim.x) {
+  for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < NN; e += (size_t)gridDim.x * blockDim.x) {
     const double g = raw[e];
     a0 += g;
     a1 += g * Wo[e];
@@ -392,9 +394,34 @@ __global__ void grad_j_kernel(const float* __restrict__ raw, const float* __rest
     __syncthreads();
   }
   if (threadIdx.x == 0) {
-    grad_J[0] = (float)s0[0];
-    grad_J[1] = (float)s1[0];
+    partial[2 * blockIdx.x] = s0[0];
+    partial[2 * blockIdx.x + 1] = s1[0];
   }
+}
+__global__ void grad_j_finish_kernel(const double* __restrict__ partial, int nblocks, float* grad_J) {
+  if (threadIdx.x == 0) {
+    double a0 = 0.0, a1 = 0.0;
+    for (int b = 0; b < nblocks; ++b) {
+      a0 += partial[2 * b];
+      a1 += partial[2 * b + 1];
+    }
+    grad_J[0] = (float)a0;
+    grad_J[1] = (float)a1;
+  }
+}
+// `scratch` needs GRAD_J_BLOCKS * 2 doubles
+int launch_grad_j(const float* raw, const float* Wo, size_t NN, float* grad_J, double* scratch, cudaStream_t s) {
+  {
+    LaunchScope ls(K_REDUCE, s);
+    grad_j_partial_kernel<<<GRAD_J_BLOCKS, 256, 0, s>>>(raw, Wo, NN, scratch);
+  }
+  RINGRNN_CUDA_TRY(cudaGetLastError());
+  {
+    LaunchScope ls(K_REDUCE, s);
+    grad_j_finish_kernel<<<1, 32, 0, s>>>(scratch, GRAD_J_BLOCKS, grad_J);
+  }
+  RINGRNN_CUDA_TRY(cudaGetLastError());
+  return RINGRNN_OK;
 }
 
 namespace {
@@ -484,11 +511,17 @@ size_t fp32_fwd_workspace_bytes(const RingRnnProblem& p) {
 size_t fp32_saved_bytes(const RingRnnProblem& p, int history_given) {
   return history_given ? 0 : align_up(sizeof(float) * (size_t)p.T * p.B * p.N, 256);
 }
+// bytes of the split-(t,b) partial sums; never less than the scratch the dJ reduction borrows from the same region
+static size_t partial_bytes(const RingRnnProblem& p, int n_mat) {
+  const size_t b = sizeof(float) * (size_t)pick_ksplit(p, n_mat) * n_mat * p.N * p.N;
+  const size_t min_b = sizeof(double) * 2 * GRAD_J_BLOCKS;
+  return align_up(b > min_b ? b : min_b, 256);
+}
 size_t fp32_bwd_workspace_bytes(const RingRnnProblem& p) {
   const int n_mat = n_mat_of(p);
   const size_t NN = (size_t)p.N * p.N;
   return align_up(sizeof(float) * n_mat * NN, 256) + align_up(sizeof(float) * (size_t)p.T * p.B * p.N, 256) +
-         align_up(sizeof(float) * (size_t)pick_ksplit(p, n_mat) * n_mat * NN, 256) + align_up(sizeof(float) * NN, 256);
+         partial_bytes(p, n_mat) + align_up(sizeof(float) * NN, 256);
 }
 
 int fp32_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) {
@@ -526,7 +559,7 @@ int fp32_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   float* delta = reinterpret_cast<float*>(w);
   w += align_up(sizeof(float) * (size_t)p.T * p.B * p.N, 256);
   float* partial = reinterpret_cast<float*>(w);
-  w += align_up(sizeof(float) * (size_t)ksplit * n_mat * NN, 256);
+  w += partial_bytes(p, n_mat);
   float* raw = reinterpret_cast<float*>(w);
 
   int rc = launch_transpose(dp, WT, s);
@@ -548,8 +581,9 @@ int fp32_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   { LaunchScope ls(K_REDUCE, s); dw_reduce_kernel<<<296, 256, 0, s>>>(dp, partial, ksplit, a.grad_Wa, a.grad_Wo, raw); }
   RINGRNN_CUDA_TRY(cudaGetLastError());
   if (a.grad_J != nullptr) {
-    { LaunchScope ls(K_REDUCE, s); grad_j_kernel<<<1, 1024, 0, s>>>(raw, p.Wo, NN, a.grad_J); }
-    RINGRNN_CUDA_TRY(cudaGetLastError());
+    // the split-(t,b) partials are dead after the reduction above: their storage serves as scratch
+    rc = launch_grad_j(raw, p.Wo, NN, a.grad_J, reinterpret_cast<double*>(partial), s);
+    if (rc != RINGRNN_OK) return rc;
   }
   return RINGRNN_OK;
 }
