@@ -17,12 +17,6 @@ namespace ringrnn {
 
 using namespace tcr;
 
-struct TcFwdParams;
-struct TcBwdParams;
-int tc_forward_launch(int act, int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmR0, const void* params,
-                      cudaStream_t s);
-int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmDL, const void* params,
-                       cudaStream_t s);
 
 namespace {
 
@@ -130,21 +124,6 @@ size_t bf16_saved_bytes(const RingRnnProblem& p) {
   return (size_t)(2 * p.T + 1) * l.state_bytes + sign_mask_bytes(p, l);
 }
 
-struct TcFwdParamsHost {
-  int B, T, N, BP, a_dim, colL, colR, n_tiles;
-  float J0, J1, alpha;
-  const float* A;
-  const float* r_init;
-  __nv_bfloat16* Rh;
-  __nv_bfloat16* Dh;
-  uint32_t* Sg;
-  float* hist;
-  float* dec_part;
-  const float* dec_u;
-  const float* dec_v;
-  float* final_state;
-  int* status;
-};
 
 int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) {
   const RingRnnProblem& p = a.p;
@@ -187,7 +166,7 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
     return RINGRNN_ERR_CUDA;
 
   const bool want_dec = a.dec_x || a.dec_y || a.dec_ta;
-  TcFwdParamsHost fp;
+  TcFwdParams fp;
   memset(&fp, 0, sizeof(fp));
   fp.B = p.B; fp.T = p.T; fp.N = p.N; fp.BP = l.BP; fp.a_dim = p.a_dim;
   fp.colL = dp.n_mat > 1 ? dp.cols[0] : -1;
@@ -201,7 +180,7 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   fp.dec_u = a.dec_u; fp.dec_v = a.dec_v;
   fp.final_state = a.final_state;
   fp.status = status;
-  int rc = tc_forward_launch(p.activation, l.NP, l.pair, tmW, tmR0, &fp, s);
+  int rc = tc_forward_launch(p.activation, l.NP, l.pair, tmW, tmR0, fp, s);
   if (rc != RINGRNN_OK) return rc;
   if (want_dec) {
     LaunchScope ls(K_LOSS, s);
@@ -263,22 +242,6 @@ size_t bf16_bwd_workspace_bytes(const RingRnnProblem& p) {
   return 1024 + b.w_bytes + b.dl_bytes + b.partial_bytes + b.dw_bytes + b.raw_bytes;
 }
 
-struct TcBwdParamsHost {
-  int B, T, N, BP, a_dim, colL, colR, n_tiles;
-  float J0, J1, alpha;
-  const float* A;
-  const __nv_bfloat16* Dh;
-  const uint32_t* Sg;
-  const float* grad_output;
-  const float* coef_x;
-  const float* coef_y;
-  const float* coef_s;
-  const float* dec_u;
-  const float* dec_v;
-  __nv_bfloat16* DL;
-  float* grad_r_init;
-  int* status;
-};
 
 int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s) {
   const RingRnnProblem& p = a.p;
@@ -316,7 +279,7 @@ int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   if (!make_tmap_bf16_2d(&tmW, Wb, (uint64_t)l.C * 2 * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, 64))
     return RINGRNN_ERR_CUDA;
 
-  TcBwdParamsHost bp;
+  TcBwdParams bp;
   memset(&bp, 0, sizeof(bp));
   bp.B = p.B; bp.T = p.T; bp.N = p.N; bp.BP = l.BP; bp.a_dim = p.a_dim;
   bp.colL = colL; bp.colR = colR;
@@ -332,7 +295,7 @@ int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   bp.status = status;
   CUtensorMap tmDL;
   if (!make_tmap_bf16_2d(&tmDL, DL, (uint64_t)p.T * l.BP, (uint64_t)3 * l.NP, 128, 64)) return RINGRNN_ERR_CUDA;
-  int rc = tc_backward_launch(l.NP, l.pair, tmW, tmDL, &bp, s);
+  int rc = tc_backward_launch(l.NP, l.pair, tmW, tmDL, bp, s);
   if (rc != RINGRNN_OK) return rc;
 
   // dWcat[3NP, NP] = DL^T [3NP, T*BP] x Rh[0..T) [T*BP, NP]

@@ -19,22 +19,6 @@ namespace ringrnn {
 using namespace tc;
 using namespace tcr;
 
-struct TcBwdParams {
-  int B, T, N, BP, a_dim, colL, colR, n_tiles;
-  float J0, J1, alpha;
-  const float* A;               // [B,T,a_dim]
-  const __nv_bfloat16* Dh;      // F'(re_t), blocked layout (tc_recurrent.cuh)
-  const uint32_t* Sg;           // [T][NP/32][2][BP] sign masks of r_t
-  const float* grad_output;     // [T,B,N] or nullptr
-  const float* coef_x;          // [B,T] or nullptr
-  const float* coef_y;
-  const float* coef_s;
-  const float* dec_u;           // [N]
-  const float* dec_v;
-  __nv_bfloat16* DL;            // [T*BP][3*NP]
-  float* grad_r_init;           // [B,N] or nullptr
-  int* status;
-};
 
 template <int NP, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -271,9 +255,8 @@ static int launch_bwd_tc(const CUtensorMap& tmW, const CUtensorMap& tmDL, const 
   return RINGRNN_OK;
 }
 
-int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmDL, const void* params,
+int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmDL, const TcBwdParams& p,
                        cudaStream_t s) {
-  const TcBwdParams& p = *static_cast<const TcBwdParams*>(params);  // same field order as the host-side mirror
   if (NP == 128) return pair ? launch_bwd_tc<128, true>(tmW, tmDL, p, s) : launch_bwd_tc<128, false>(tmW, tmDL, p, s);
   if (NP == 256) return pair ? launch_bwd_tc<256, true>(tmW, tmDL, p, s) : launch_bwd_tc<256, false>(tmW, tmDL, p, s);
   if (NP == 512) return pair ? launch_bwd_tc<512, true>(tmW, tmDL, p, s) : launch_bwd_tc<512, false>(tmW, tmDL, p, s);

@@ -17,21 +17,6 @@ namespace ringrnn {
 using namespace tc;
 using namespace tcr;
 
-struct TcFwdParams {
-  int B, T, N, BP, a_dim, colL, colR, n_tiles;  // n_tiles = BP / (128 or, for CTA pairs, 256)
-  float J0, J1, alpha;
-  const float* A;        // [B,T,a_dim]
-  const float* r_init;   // [B,N]
-  __nv_bfloat16* Rh;     // [T+1][BP][NP] (slot 0 = bf16(r_init), prepared before launch) or nullptr
-  __nv_bfloat16* Dh;     // F'(re_t), blocked layout (tc_recurrent.cuh), T*BP*NP elements, or nullptr
-  uint32_t* Sg;          // [T][NP/32][2][BP] bit masks of r_t > 0 and r_t < 0 (bit j = neuron 32*block + j), or nullptr
-  float* hist;           // [T,B,N] or nullptr
-  float* dec_part;       // [2C][3][T][BP] or nullptr
-  const float* dec_u;    // [N]
-  const float* dec_v;
-  float* final_state;    // [B,N] or nullptr
-  int* status;
-};
 
 template <int ACT, int NP, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -240,9 +225,8 @@ static int launch_fwd_tc(const CUtensorMap& tmW, const CUtensorMap& tmR0, const 
   return RINGRNN_OK;
 }
 
-int tc_forward_launch(int act, int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmR0, const void* params,
+int tc_forward_launch(int act, int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmR0, const TcFwdParams& p,
                       cudaStream_t s) {
-  const TcFwdParams& p = *static_cast<const TcFwdParams*>(params);  // same field order as the host-side mirror
 #define RINGRNN_TCF(ACT, NPV)                                                              \
   if (act == ACT && NP == NPV)                                                             \
     return pair ? launch_fwd_tc<ACT, NPV, true>(tmW, tmR0, p, s) : launch_fwd_tc<ACT, NPV, false>(tmW, tmR0, p, s);

@@ -53,6 +53,45 @@ static __device__ long long g_timeline[64 * 16];  // one copy per translation un
 #define RINGRNN_STAMP_VAL(step, slot, v) do {} while (0)
 #endif
 
+// Kernel parameters of the two recurrent kernels (filled by ringrnn_bf16.cu).
+struct TcFwdParams {
+  int B, T, N, BP, a_dim, colL, colR, n_tiles;  // n_tiles = BP / (128 or, for CTA pairs, 256)
+  float J0, J1, alpha;
+  const float* A;        // [B,T,a_dim]
+  const float* r_init;   // [B,N]
+  __nv_bfloat16* Rh;     // [T+1][BP][NP] (slot 0 = bf16(r_init), prepared before launch) or nullptr
+  __nv_bfloat16* Dh;     // F'(re_t), blocked layout (tc_recurrent.cuh), T*BP*NP elements, or nullptr
+  uint32_t* Sg;          // [T][NP/32][2][BP] bit masks of r_t > 0 and r_t < 0 (bit j = neuron 32*block + j), or nullptr
+  float* hist;           // [T,B,N] or nullptr
+  float* dec_part;       // [2C][3][T][BP] or nullptr
+  const float* dec_u;    // [N]
+  const float* dec_v;
+  float* final_state;    // [B,N] or nullptr
+  int* status;
+};
+
+struct TcBwdParams {
+  int B, T, N, BP, a_dim, colL, colR, n_tiles;
+  float J0, J1, alpha;
+  const float* A;               // [B,T,a_dim]
+  const __nv_bfloat16* Dh;      // F'(re_t), blocked layout (tc_recurrent.cuh)
+  const uint32_t* Sg;           // [T][NP/32][2][BP] sign masks of r_t
+  const float* grad_output;     // [T,B,N] or nullptr
+  const float* coef_x;          // [B,T] or nullptr
+  const float* coef_y;
+  const float* coef_s;
+  const float* dec_u;           // [N]
+  const float* dec_v;
+  __nv_bfloat16* DL;            // [T*BP][3*NP]
+  float* grad_r_init;           // [B,N] or nullptr
+  int* status;
+};
+
+int tc_forward_launch(int act, int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmR0, const TcFwdParams& p,
+                      cudaStream_t s);
+int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmDL, const TcBwdParams& p,
+                       cudaStream_t s);
+
 namespace tcr {
 
 constexpr int CHUNK_BYTES = 128 * 128;  // one [128 samples x 64 neurons] bf16 chunk
