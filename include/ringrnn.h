@@ -100,7 +100,10 @@ typedef struct RingRnnFwdArgs {
  *   bump_history  the forward output when it was written; NULL = use `saved`
  *   grad_Wa [a_dim,N,N], grad_Wo [N,N]  fp32 out, overwritten (cpp/ring_rnn_cuda.py:98-99, :144)
  *   grad_J        float[2] out = {dL/dJ0, dL/dJ1}, NULL = skip (the reference returns None)
- *   grad_r_init   [B,N] out, NULL = skip (the reference returns None) */
+ *   grad_r_init   [B,N] out, NULL = skip (the reference returns None)
+ *   grad_A        [B,T,a_dim] out = dL/dA, NULL = skip (the reference returns None; needed by models whose action
+ *                 signal comes from trainable gain networks, train/train_ring_attractor.py:131-146).  Columns that
+ *                 n_active / active_cols leave out receive zero: pass n_active < 0 to get every column. */
 typedef struct RingRnnBwdArgs {
   RingRnnProblem p;
   const float* grad_output;
@@ -116,6 +119,7 @@ typedef struct RingRnnBwdArgs {
   float* grad_Wo;
   float* grad_J;
   float* grad_r_init;
+  float* grad_A;
   void* workspace;
   size_t workspace_bytes;
   int* status;

@@ -40,8 +40,8 @@ class BwdArgs(C.Structure):
                 ("coef_s", C.c_void_p), ("dec_u", C.c_void_p), ("dec_v", C.c_void_p),
                 ("bump_history", C.c_void_p), ("saved", C.c_void_p), ("saved_bytes", C.c_size_t),
                 ("grad_Wa", C.c_void_p), ("grad_Wo", C.c_void_p), ("grad_J", C.c_void_p),
-                ("grad_r_init", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-                ("status", C.c_void_p)]
+                ("grad_r_init", C.c_void_p), ("grad_A", C.c_void_p), ("workspace", C.c_void_p),
+                ("workspace_bytes", C.c_size_t), ("status", C.c_void_p)]
 
 
 # every symbol include/ringrnn.h declares: name -> (restype, argtypes)

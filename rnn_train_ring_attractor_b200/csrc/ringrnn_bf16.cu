@@ -218,9 +218,25 @@ int gemm_splits(const Layout& l, int T) {
 }
 
 struct BwdLayout {
-  size_t w_bytes, dl_bytes, partial_bytes, dw_bytes, raw_bytes;
+  size_t w_bytes, dl_bytes, partial_bytes, dw_bytes, raw_bytes, da_bytes;
   int nsplit;
 };
+
+// grad_A[b,t,col] = sum over slots of part[slot][k][t][b], k = 0 -> colL, k = 1 -> colR
+__global__ void da_reduce_kernel(const float* __restrict__ part, int slots, int B, int T, int BP, int a_dim, int colL,
+                                 int colR, float* grad_A) {
+  const size_t total = (size_t)B * T;
+  for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / B), b = (int)(idx % B);
+    float acc[2] = {0.f, 0.f};
+    for (int sl = 0; sl < slots; ++sl)
+#pragma unroll
+      for (int k = 0; k < 2; ++k) acc[k] += part[(((size_t)sl * 2 + k) * T + t) * BP + b];
+    float* o = grad_A + ((size_t)b * T + t) * a_dim;
+    if (colL >= 0) o[colL] = acc[0];
+    if (colR >= 0) o[colR] = acc[1];
+  }
+}
 
 BwdLayout bwd_layout_of(const RingRnnProblem& p, const Layout& l) {
   BwdLayout b;
@@ -230,16 +246,17 @@ BwdLayout bwd_layout_of(const RingRnnProblem& p, const Layout& l) {
   b.partial_bytes = align_up((size_t)b.nsplit * 3 * l.NP * l.NP * 4, 1024);
   b.dw_bytes = align_up((size_t)3 * l.NP * l.NP * 4, 1024);
   b.raw_bytes = align_up((size_t)p.N * p.N * 4, 1024);
+  b.da_bytes = align_up((size_t)2 * l.C * 2 * p.T * l.BP * 4, 1024);
   return b;
 }
 
 }  // namespace
 
-// BWD workspace: status(1024) | Wb | DL | split-K partials | dWcat | raw
+// BWD workspace: status(1024) | Wb | DL | split-K partials | dWcat | raw | dL/dA partials
 size_t bf16_bwd_workspace_bytes(const RingRnnProblem& p) {
   const Layout l = layout_of(p);
   const BwdLayout b = bwd_layout_of(p, l);
-  return 1024 + b.w_bytes + b.dl_bytes + b.partial_bytes + b.dw_bytes + b.raw_bytes;
+  return 1024 + b.w_bytes + b.dl_bytes + b.partial_bytes + b.dw_bytes + b.raw_bytes + b.da_bytes;
 }
 
 
@@ -263,6 +280,8 @@ int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   float* dWcat = reinterpret_cast<float*>(w);
   w += bl.dw_bytes;
   float* raw = reinterpret_cast<float*>(w);
+  w += bl.raw_bytes;
+  float* dA_part = reinterpret_cast<float*>(w);
   const __nv_bfloat16* Rh = static_cast<const __nv_bfloat16*>(a.saved);
   const __nv_bfloat16* Dh = Rh + (size_t)(p.T + 1) * l.BP * l.NP;
 
@@ -292,12 +311,20 @@ int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   bp.dec_u = a.dec_u; bp.dec_v = a.dec_v;
   bp.DL = DL;
   bp.grad_r_init = a.grad_r_init;
+  bp.Rh = Rh;
+  bp.dA_part = a.grad_A != nullptr ? dA_part : nullptr;
   bp.status = status;
   CUtensorMap tmDL;
   if (!make_tmap_bf16_2d(&tmDL, DL, (uint64_t)p.T * l.BP, (uint64_t)3 * l.NP, 128, 64)) return RINGRNN_ERR_CUDA;
   int rc = tc_backward_launch(l.NP, l.pair, tmW, tmDL, bp, s);
   if (rc != RINGRNN_OK) return rc;
 
+  if (a.grad_A != nullptr) {
+    RINGRNN_CUDA_TRY(cudaMemsetAsync(a.grad_A, 0, sizeof(float) * (size_t)p.B * p.T * p.a_dim, s));
+    LaunchScope ls(K_REDUCE, s);
+    da_reduce_kernel<<<296, 256, 0, s>>>(dA_part, 2 * l.C, p.B, p.T, l.BP, p.a_dim, colL, colR, a.grad_A);
+    RINGRNN_CUDA_TRY(cudaGetLastError());
+  }
   // dWcat[3NP, NP] = DL^T [3NP, T*BP] x Rh[0..T) [T*BP, NP]
   rc = tc_gemm(1, DL, Rh, partial, dWcat, 3 * l.NP, l.NP, (long long)p.T * l.BP, bl.nsplit, status, s);
   if (rc != RINGRNN_OK) return rc;

@@ -175,6 +175,7 @@ struct Fp32BwdIn {
   const float* dec_v;
   float* delta;              // [T,B,N] out
   float* grad_r_init;        // [B,N] or nullptr
+  float* grad_A;             // [B,T,a_dim] or nullptr (columns of inactive matrices are zeroed by the host)
 };
 
 template <int ACT, int BT>
@@ -188,8 +189,11 @@ __global__ void __launch_bounds__(FT) bwd_fp32_kernel(DevProblem p, const float*
   float* cf = sc + p.n_mat * BT;            // [3][BT] loss coefficients of this step
   float* red = cf + 3 * BT;                 // [FT/BT][BT][4]
   float* stats = red + (FT / BT) * BT * 4;  // [BT][4]
+  float* dacc = stats + BT * 4;             // [n_mat][BT][FT/32] per-warp sums for dL/dA
   const int b0 = blockIdx.x * BT;
   const bool has_coef = in.coef_x != nullptr;
+  const bool want_dA = in.grad_A != nullptr;
+  const int warp_id = threadIdx.x >> 5, lane_id = threadIdx.x & 31;
 
   for (int idx = threadIdx.x; idx < N * BT; idx += FT) gs[idx] = 0.f;
 
@@ -209,6 +213,8 @@ __global__ void __launch_bounds__(FT) bwd_fp32_kernel(DevProblem p, const float*
       }
       cf[threadIdx.x] = v;
     }
+    if (want_dA)
+      for (int idx = threadIdx.x; idx < p.n_mat * BT * (FT / 32); idx += FT) dacc[idx] = 0.f;
     __syncthreads();
     state_stats<BT>(rp, N, nullptr, nullptr, red, stats);
     // phase 1: recompute re_t, form g_t and delta_t for the neurons this thread owns
@@ -241,36 +247,62 @@ __global__ void __launch_bounds__(FT) bwd_fp32_kernel(DevProblem p, const float*
     __syncthreads();
     state_stats<BT>(ds, N, nullptr, nullptr, red, stats);
     // phase 2: carry_{t-1}[b,j] = (1-alpha) g + J0*sum_i delta + sum_m sc_m * sum_i delta[b,i] W_m[i,j]
-    for (int j = threadIdx.x; j < N; j += FT) {
+    // (uniform trip count: the dL/dA sums below use warp shuffles)
+    for (int j0 = 0; j0 < N; j0 += FT) {
+      const int j = j0 + threadIdx.x;
+      const bool live = j < N;
       float acc[BT];
 #pragma unroll
-      for (int b = 0; b < BT; ++b) acc[b] = fmaf(p.J0, stats[b * 4], (1.f - p.alpha) * gs[j * BT + b]);
+      for (int b = 0; b < BT; ++b) acc[b] = live ? fmaf(p.J0, stats[b * 4], (1.f - p.alpha) * gs[j * BT + b]) : 0.f;
       // m = 0 is Wo, m >= 1 are the active Wa matrices, all in their original [i][j] layout
       for (int m = 0; m < p.n_mat; ++m) {
         const float* W = (m == 0) ? p.Wo : p.Wa + (size_t)p.cols[m - 1] * N * N;
         float tmp[BT];
 #pragma unroll
         for (int b = 0; b < BT; ++b) tmp[b] = 0.f;
+        if (live) {
 #pragma unroll 4
-        for (int i = 0; i < N; ++i) {
-          const float wv = __ldg(W + (size_t)i * N + j);
-          const float4* s4 = reinterpret_cast<const float4*>(ds + i * BT);
+          for (int i = 0; i < N; ++i) {
+            const float wv = __ldg(W + (size_t)i * N + j);
+            const float4* s4 = reinterpret_cast<const float4*>(ds + i * BT);
 #pragma unroll
-          for (int b4 = 0; b4 < BT / 4; ++b4) {
-            const float4 s = s4[b4];
-            tmp[b4 * 4 + 0] = fmaf(s.x, wv, tmp[b4 * 4 + 0]);
-            tmp[b4 * 4 + 1] = fmaf(s.y, wv, tmp[b4 * 4 + 1]);
-            tmp[b4 * 4 + 2] = fmaf(s.z, wv, tmp[b4 * 4 + 2]);
-            tmp[b4 * 4 + 3] = fmaf(s.w, wv, tmp[b4 * 4 + 3]);
+            for (int b4 = 0; b4 < BT / 4; ++b4) {
+              const float4 s = s4[b4];
+              tmp[b4 * 4 + 0] = fmaf(s.x, wv, tmp[b4 * 4 + 0]);
+              tmp[b4 * 4 + 1] = fmaf(s.y, wv, tmp[b4 * 4 + 1]);
+              tmp[b4 * 4 + 2] = fmaf(s.z, wv, tmp[b4 * 4 + 2]);
+              tmp[b4 * 4 + 3] = fmaf(s.w, wv, tmp[b4 * 4 + 3]);
+            }
           }
         }
 #pragma unroll
         for (int b = 0; b < BT; ++b) acc[b] = fmaf(sc[m * BT + b], tmp[b], acc[b]);
-      }
+        if (want_dA && m > 0) {
+          // dL/dA[b,t,k] = sum_j r_{t-1}[b,j] * (delta_t W_k)[b,j]: per-warp sums in fixed order, one writer per slot
 #pragma unroll
-      for (int b = 0; b < BT; ++b) gs[j * BT + b] = acc[b];
+          for (int b = 0; b < BT; ++b) {
+            float v = live ? rp[j * BT + b] * tmp[b] : 0.f;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+            if (lane_id == 0) dacc[(m * BT + b) * (FT / 32) + warp_id] += v;
+          }
+        }
+      }
+      if (live) {
+#pragma unroll
+        for (int b = 0; b < BT; ++b) gs[j * BT + b] = acc[b];
+      }
     }
     __syncthreads();
+    if (want_dA) {
+      for (int idx = threadIdx.x; idx < (p.n_mat - 1) * BT; idx += FT) {
+        const int m = 1 + idx / BT, b = idx % BT;
+        float v = 0.f;
+        for (int w = 0; w < FT / 32; ++w) v += dacc[(m * BT + b) * (FT / 32) + w];
+        if (b0 + b < p.B) in.grad_A[((size_t)(b0 + b) * p.T + t) * p.a_dim + p.cols[m - 1]] = v;
+      }
+      __syncthreads();  // dacc is zeroed at the top of the next step
+    }
   }
   if (in.grad_r_init != nullptr) {
     for (int idx = threadIdx.x; idx < N * BT; idx += FT) {
@@ -442,7 +474,8 @@ size_t fwd_smem(int N, int n_mat, int BT) {
   return sizeof(float) * ((size_t)2 * N * BT + (size_t)n_mat * BT + (FT / BT) * BT * 4 + BT * 4);
 }
 size_t bwd_smem(int N, int n_mat, int BT) {
-  return sizeof(float) * ((size_t)3 * N * BT + (size_t)n_mat * BT + 3 * BT + (FT / BT) * BT * 4 + BT * 4);
+  return sizeof(float) * ((size_t)3 * N * BT + (size_t)n_mat * BT + 3 * BT + (FT / BT) * BT * 4 + BT * 4 +
+                          (size_t)n_mat * BT * (FT / 32));
 }
 constexpr size_t SMEM_MAX = 227 * 1024;
 
@@ -564,7 +597,9 @@ int fp32_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
 
   int rc = launch_transpose(dp, WT, s);
   if (rc != RINGRNN_OK) return rc;
-  Fp32BwdIn in{hist, a.grad_output, a.coef_x, a.coef_y, a.coef_s, a.dec_u, a.dec_v, delta, a.grad_r_init};
+  if (a.grad_A != nullptr)
+    RINGRNN_CUDA_TRY(cudaMemsetAsync(a.grad_A, 0, sizeof(float) * (size_t)p.B * p.T * p.a_dim, s));
+  Fp32BwdIn in{hist, a.grad_output, a.coef_x, a.coef_y, a.coef_s, a.dec_u, a.dec_v, delta, a.grad_r_init, a.grad_A};
   if (bwd_smem(p.N, n_mat, 16) <= SMEM_MAX) rc = launch_bwd<16>(dp, p.activation, WT, in, s);
   else if (bwd_smem(p.N, n_mat, 8) <= SMEM_MAX) rc = launch_bwd<8>(dp, p.activation, WT, in, s);
   else if (bwd_smem(p.N, n_mat, 4) <= SMEM_MAX) rc = launch_bwd<4>(dp, p.activation, WT, in, s);

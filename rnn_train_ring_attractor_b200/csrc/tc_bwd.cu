@@ -55,6 +55,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     const int nq = q * 128 + 32 * h;
     const float J0 = p.J0, J1 = p.J1, alpha = p.alpha, beta = 1.f - p.alpha;
     const bool has_coef = p.coef_x != nullptr;
+    const bool want_dA = p.dA_part != nullptr;
     uint32_t g = 0;
     for (int tile = cluster_id; tile < p.n_tiles; tile += n_clusters) {
       const int b = tile * C_::TILE_ROWS + c.half * 128 + row;
@@ -176,7 +177,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       produce(T - 1);
       for (int t = T - 1; t >= 0; --t, ++g) {
         if (t > 0) prefetch(t - 1);
-        float c0 = 0.f;
+        float c0 = 0.f, dAl = 0.f, dAr = 0.f;
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
           mbar_wait(bars + OFF_D_FULL + 8 * s, g & 1u, wctx, 307);
@@ -196,6 +197,18 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             tmem_ld16(col + 64, zl);
             tmem_ld16(col + 128, zr);
             tmem_ld_wait();
+            if (want_dA) {
+              // dL/dL_t = sum_j r_{t-1}[j] (delta_t Wl)[j], likewise for R: this thread's 16 columns
+              const uint4* rsrc = reinterpret_cast<const uint4*>(p.Rh + ((size_t)t * p.BP + b) * NP + nq + 64 * s + 16 * c16);
+              const uint4 r0 = __ldg(rsrc), r1 = __ldg(rsrc + 1);
+              const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float rp = (j & 1) ? bf16_hi(rw[j >> 1]) : bf16_lo(rw[j >> 1]);
+                dAl = fmaf(rp, __uint_as_float(zl[j]), dAl);
+                dAr = fmaf(rp, __uint_as_float(zr[j]), dAr);
+              }
+            }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int idx = s * 32 + c16 * 16 + j;
@@ -208,6 +221,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           }
           release_accumulator<NP, PAIR>(c, s, lane);
           if (warp == 4 && lane == 0) RINGRNN_STAMP(g, s == 0 ? 6 : 8);
+        }
+        if (want_dA) {
+          float* dp = p.dA_part + (((size_t)(2 * q + h) * 2) * T + t) * p.BP + b;
+          dp[0] = dAl;
+          dp[(size_t)T * p.BP] = dAr;
         }
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 9);
         mbar_wait<true>(bars + OFF_ALL_FREE, g & 1u, wctx, 308);

@@ -84,6 +84,8 @@ struct TcBwdParams {
   const float* dec_v;
   __nv_bfloat16* DL;            // [T*BP][3*NP]
   float* grad_r_init;           // [B,N] or nullptr
+  const __nv_bfloat16* Rh;      // [T+1][BP][NP] saved state (read only when dA_part is set)
+  float* dA_part;               // [2C][2][T][BP] partial sums of dL/dL_t and dL/dR_t, or nullptr
   int* status;
 };
 

@@ -51,7 +51,7 @@ class RingRnnFusedFunc(Function):
         if target.shape != (B, T):
             raise RuntimeError("target_angle must be (batch, seq_len)")
         dev = action_signal.device
-        active = active_columns(action_signal)
+        active = list(range(a_dim)) if ctx.needs_input_grad[0] else active_columns(action_signal)
         prec = choose_precision(B, T, N, a_dim, act, len(active), precision)
         if inv_count is None:
             inv_count = 1.0 / (B * T)
@@ -97,6 +97,7 @@ class RingRnnFusedFunc(Function):
         dev = action_signal.device
         want_j = any(torch.is_tensor(j) and j.requires_grad for j in (ctx.J0, ctx.J1)) or ctx.grad_buffer is not None
         want_r = ctx.needs_input_grad[5]
+        want_a = ctx.needs_input_grad[0]
         L = _lib.lib()
         with torch.cuda.device(dev):
             p = _lib.make_problem(B, T, N, a_dim, ctx.act, ctx.prec, _scalar(ctx.J0), _scalar(ctx.J1), ctx.alpha,
@@ -113,9 +114,11 @@ class RingRnnFusedFunc(Function):
                 grad_Wo = torch.empty_like(Wo)
                 grad_J = torch.empty(2, device=dev, dtype=torch.float32) if want_j else None
             grad_r = torch.empty_like(r_init) if want_r else None
+            grad_a = torch.empty_like(action_signal) if want_a else None
             ws = _scratch(L.ringrnn_workspace_bytes(C.byref(p), _lib.WS_BWD, 0), dev)
             a = _lib.BwdArgs()
             a.p = p
+            a.grad_A = None if grad_a is None else grad_a.data_ptr()
             a.coef_x, a.coef_y, a.coef_s = scal[3].data_ptr(), scal[4].data_ptr(), scal[5].data_ptr()
             a.dec_u, a.dec_v = u.data_ptr(), v.data_ptr()
             a.saved, a.saved_bytes = saved.data_ptr(), saved.numel()
@@ -135,9 +138,11 @@ class RingRnnFusedFunc(Function):
                     grad_J.mul_(g_loss)
             if grad_r is not None:
                 grad_r.mul_(g_loss)
+            if grad_a is not None:
+                grad_a.mul_(g_loss)
         gJ0 = grad_J[0].reshape(ctx.J0.shape) if (torch.is_tensor(ctx.J0) and ctx.J0.requires_grad) else None
         gJ1 = grad_J[1].reshape(ctx.J1.shape) if (torch.is_tensor(ctx.J1) and ctx.J1.requires_grad) else None
-        return (None, grad_Wa, gJ0, gJ1, grad_Wo, grad_r, None, None, None, None, None, None, None)
+        return (grad_a, grad_Wa, gJ0, gJ1, grad_Wo, grad_r, None, None, None, None, None, None, None)
 
 
 def ring_rnn_fused(action_signal, Wa, J0, J1, Wo, r_init, alpha, activation, target_angle, bump_weight=0.2,

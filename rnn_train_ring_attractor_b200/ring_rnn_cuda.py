@@ -9,7 +9,9 @@ Same names, argument order, return layout and error behaviour:
 obtains `torch` through `from cpp.ring_rnn_cuda import *` (train_general_ring_no_gain.py:1-19).
 
 Extensions beyond the reference (all optional): J0 / J1 may be 0-dim tensors that require grad (their
-gradients are then returned instead of None), and r_init receives its gradient when it requires one.
+gradients are then returned instead of None), and r_init and action_signal receive their gradients when they
+require them (the reference returns None for all four, cpp/ring_rnn_cuda.py:144).  The action-signal gradient is
+what the gain-network models (train/train_ring_attractor.py:131-146) need to train their gain MLPs through the op.
 Arithmetic mode: `set_precision("bf16" | "fp32" | "auto")` or the RINGRNN_PRECISION environment variable;
 "auto" takes the bf16 tensor-core path whenever it supports the shape, else the fp32 path, which is the
 reference's own dispatch rule in spirit (cpp/fwd.cu:36).
@@ -121,7 +123,8 @@ class RingRnnCudaFunc(Function):
         if Wa.shape != (a_dim, N, N) or Wo.shape != (N, N) or r_init.shape != (batch_size, N):
             raise RuntimeError("shape mismatch between action_signal, Wa, Wo and r_init")
         dev = action_signal.device
-        active = active_columns(action_signal)
+        # zero columns may be skipped only if nobody asks for the gradient with respect to the action signal
+        active = list(range(a_dim)) if ctx.needs_input_grad[0] else active_columns(action_signal)
         prec = choose_precision(batch_size, seq_len, N, a_dim, act, len(active))
         L = _lib.lib()
         with torch.cuda.device(dev):
@@ -157,6 +160,7 @@ class RingRnnCudaFunc(Function):
         grad_output_ctg = grad_output.contiguous()  # arrives as a permuted view from the model's decode
         want_j = any(torch.is_tensor(j) and j.requires_grad for j in (ctx.J0, ctx.J1))
         want_r = ctx.needs_input_grad[5]
+        want_a = ctx.needs_input_grad[0]
         L = _lib.lib()
         with torch.cuda.device(dev):
             p = _lib.make_problem(batch_size, seq_len, N, a_dim, act, ctx.prec, _scalar(ctx.J0), _scalar(ctx.J1),
@@ -166,9 +170,11 @@ class RingRnnCudaFunc(Function):
             grad_Wo = torch.empty_like(Wo)
             grad_J = torch.empty(2, device=dev, dtype=torch.float32) if want_j else None
             grad_r = torch.empty_like(r_init) if want_r else None
+            grad_a = torch.empty_like(action_signal) if want_a else None
             ws = _scratch(L.ringrnn_workspace_bytes(C.byref(p), _lib.WS_BWD, 1), dev)
             a = _lib.BwdArgs()
             a.p = p
+            a.grad_A = None if grad_a is None else grad_a.data_ptr()
             a.grad_output = grad_output_ctg.data_ptr()
             a.bump_history = bump_history.data_ptr()
             a.saved, a.saved_bytes = saved.data_ptr(), saved.numel()
@@ -181,4 +187,4 @@ class RingRnnCudaFunc(Function):
                 _lib.check_device_status(ws, "backward")
         gJ0 = grad_J[0].reshape(ctx.J0.shape) if (torch.is_tensor(ctx.J0) and ctx.J0.requires_grad) else None
         gJ1 = grad_J[1].reshape(ctx.J1.shape) if (torch.is_tensor(ctx.J1) and ctx.J1.requires_grad) else None
-        return None, grad_Wa, gJ0, gJ1, grad_Wo, grad_r, None, None
+        return grad_a, grad_Wa, gJ0, gJ1, grad_Wo, grad_r, None, None

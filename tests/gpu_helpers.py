@@ -82,11 +82,12 @@ def run_backward(A, Wa, Wo, r_init, J0, J1, alpha, act, fwd, grad_output=None, c
     args = _lib.BwdArgs()
     args.p = p
     out = {"backs": []}
-    for name, shape in (("dWa", (a, N, N)), ("dWo", (N, N)), ("dJ", (2,)), ("dr_init", (B, N))):
+    for name, shape in (("dWa", (a, N, N)), ("dWo", (N, N)), ("dJ", (2,)), ("dr_init", (B, N)), ("dA", (B, T, a))):
         out[name], back = padded(shape)
         out["backs"].append(back)
     args.grad_Wa, args.grad_Wo = out["dWa"].data_ptr(), out["dWo"].data_ptr()
     args.grad_J, args.grad_r_init = out["dJ"].data_ptr(), out["dr_init"].data_ptr()
+    args.grad_A = out["dA"].data_ptr()
     if grad_output is not None:
         args.grad_output = grad_output.data_ptr()
     if coefs is not None:

@@ -6,6 +6,7 @@ Edge cases follow what the reference's dispatch distinguishes (cpp/fwd.cu:36): s
 multiples of 16, a single sample, a single step, zero-padded action columns (a_dim=16), generic action
 columns (a_dim=4), every activation.
 """
+import copy
 import math
 import os
 
@@ -100,6 +101,10 @@ def test_forward_and_backward_match_oracle(shape):
         assert abs(float(b["dJ"][1]) - float(ref["dJ1"])) < tol * max(1.0, float(G.norm()) * float(Wo.norm()))
         if pad:
             assert float(b["dWa"][2:].abs().max()) == 0.0  # skipped columns: exactly zero
+            assert orc.rel_err(b["dA"][:, :, :2], ref["dA"][:, :, :2]) < (tol if prec == "fp32" else 2 * tol), prec
+        else:
+            # gradient w.r.t. the action signal (the reference returns none); per-(b,t) scalars, no averaging
+            assert orc.rel_err(b["dA"], ref["dA"]) < (tol if prec == "fp32" else 2 * tol), prec
         # same call again: bit-identical (no atomics anywhere)
         f2 = run_forward(dA, dWa_, dWo_, dr0, J0, J1, alpha, act, prec, active, history=True, decode=False)
         b2 = run_backward(dA, dWa_, dWo_, dr0, J0, J1, alpha, act, f2, grad_output=dcot, prec=prec, active=active)
@@ -263,6 +268,54 @@ def test_reference_style_model_trains_on_the_operator():
     want = run("cpu", orc.ring_forward_ref)
     for a, b in zip(got, want):
         assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (got, want)
+
+
+def test_gain_network_model_trains_through_the_operator():
+    """The reference's LeakyRingAttractor feeds L/R through two small gain MLPs (train/train_ring_attractor.py:131-146);
+    their parameters only get gradients if the operator returns dL/d(action_signal).  One step of such a model on the
+    operator against the same model on the oracle recurrence."""
+    import cpp.ring_rnn_cuda as m
+    torch.manual_seed(3)
+    N, B, T = 64, 48, 20
+    av, angle = orc.generate_av(B, T)
+    r0 = orc.initial_bump_gaussian(angle[:, 0], N)
+    Wo0 = torch.randn(N, N) / math.sqrt(N)
+    Wa0 = torch.randn(2, N, N) / math.sqrt(N)
+    nets0 = [torch.nn.Sequential(torch.nn.Linear(1, 8), torch.nn.ReLU(), torch.nn.Linear(8, 1)) for _ in range(2)]
+
+    def run(device, fwd):
+        nets = [copy.deepcopy(n).to(device) for n in nets0]
+        Wo = Wo0.clone().to(device).requires_grad_(True)
+        Wa = Wa0.clone().to(device).requires_grad_(True)
+        a = av.to(device)
+        L = nets[0](torch.relu(-a).unsqueeze(-1)).squeeze(-1)
+        R = nets[1](torch.relu(a).unsqueeze(-1)).squeeze(-1)
+        A = torch.stack([L, R], dim=2).contiguous()
+        hist = fwd(A, Wa, -0.1, 0.1, Wo, r0.to(device), 0.15, "tanh")
+        bump = hist.permute(1, 0, 2)
+        rd = bump @ orc.w_delta7(N).to(device)
+        wave = rd / rd.max(dim=2, keepdim=True)[0]
+        phi = orc.preferred_angles(N).to(device)
+        th = torch.atan2((wave * torch.sin(phi)).sum(-1), (wave * torch.cos(phi)).sum(-1))
+        tgt = angle.to(device)
+        ta = bump.abs().sum(2)
+        loss = torch.mean((torch.cos(th) - torch.cos(tgt)) ** 2 + (torch.sin(th) - torch.sin(tgt)) ** 2) \
+            + 0.2 * torch.mean((ta - ta[:, 0:1]) ** 2)
+        loss.backward()
+        grads = [p.grad.detach().cpu().clone() for n in nets for p in n.parameters()]
+        return float(loss), grads, Wo.grad.cpu()
+
+    m.set_precision("fp32")
+    try:
+        loss_g, grads_g, dWo_g = run("cuda", m.ring_rnn_cuda_func)
+    finally:
+        m.set_precision("auto")
+    loss_c, grads_c, dWo_c = run("cpu", orc.ring_forward_ref)
+    assert abs(loss_g - loss_c) < 1e-4 * max(1.0, abs(loss_c))
+    assert orc.rel_err(dWo_g, dWo_c) < 2e-4
+    for gg, gc in zip(grads_g, grads_c):
+        assert gg.abs().sum() > 0  # the gain networks do receive gradients
+        assert orc.rel_err(gg, gc) < 5e-4
 
 
 def test_raw_extension_objects():
