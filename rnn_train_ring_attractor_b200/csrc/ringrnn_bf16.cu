@@ -1,7 +1,7 @@
 // bf16 mode of the ring-attractor operator: host orchestration of the tensor-core kernels
 // (tc_fwd.cu, tc_bwd.cu, tc_gemm.cu), operand preparation and buffer layouts.
 //
-// Layouts (NP = N rounded up to 128/256/512, BP = B rounded up to the tile height 128 (256 for CTA pairs), C = NP/128):
+// Layouts (NP = N rounded up to 128/256/512/1024, BP = B rounded up to the tile height 128 (256 for CTA pairs), C = NP/128):
 //   weights, forward  Wf [C*2*RB, NP] bf16 (RB = 208, or 224 when CTA pairs are used, i.e. B > 128): block (q,s) rows = {Wo[i,:], Wl[i,:], Wr[i,:] for the 64 neurons i of
 //                     sub-slice s of CTA q, a row of ones, zero rows}; columns j >= N zero
 //   weights, backward Wb, same shape: rows = {Wo[:,j], Wl[:,j], Wr[:,j] for the 64 neurons j, ones, zeros}
@@ -20,15 +20,15 @@ using namespace tcr;
 
 namespace {
 
-int padded_n(int N) { return N <= 128 ? 128 : (N <= 256 ? 256 : (N <= 512 ? 512 : 0)); }
+int padded_n(int N) { return N <= 128 ? 128 : (N <= 256 ? 256 : (N <= 512 ? 512 : (N <= 1024 ? 1024 : 0))); }
 // CTA pairs (tiles of 256 samples, cta_group::2 MMAs sharing every weight tile) halve the weight stream, but a B200
 // keeps at most 15 clusters of 8 CTAs resident against 33 clusters of 4, so for N = 512 the single shape finishes a
 // 4096-sample batch in one wave and pairs need two.  Pairs are therefore opt-in (RINGRNN_PAIRS=1), for experiments.
-bool use_pairs(int B) {
+bool use_pairs(int B, int N) {
   static const bool on = getenv("RINGRNN_PAIRS") != nullptr && getenv("RINGRNN_PAIRS")[0] == '1';
-  return on && B > 128;
+  return on && B > 128 && N <= 512;
 }
-int padded_b(int B) { return use_pairs(B) ? (B + 255) / 256 * 256 : (B + 127) / 128 * 128; }
+int padded_b(int B, int N) { return use_pairs(B, N) ? (B + 255) / 256 * 256 : (B + 127) / 128 * 128; }
 int n_active_of(const RingRnnProblem& p) { return p.n_active < 0 ? p.a_dim : p.n_active; }
 
 // Wf / Wb blocks, see the header comment.  grid (NP/64 column chunks, C*2 blocks), block 256
@@ -92,9 +92,9 @@ struct Layout {
 Layout layout_of(const RingRnnProblem& p) {
   Layout l;
   l.NP = padded_n(p.N);
-  l.BP = padded_b(p.B);
+  l.BP = padded_b(p.B, p.N);
   l.C = l.NP / 128;
-  l.pair = use_pairs(p.B);
+  l.pair = use_pairs(p.B, p.N);
   l.RB = block_rows(l.pair);
   l.tile_rows = l.pair ? 256 : 128;
   l.w_bytes = align_up((size_t)l.C * 2 * l.RB * l.NP * 2, 1024);
@@ -210,8 +210,8 @@ __global__ void unpack_dw_kernel(const float* __restrict__ dWcat, int N, int NP,
 }
 
 int gemm_splits(const Layout& l, int T) {
-  const int m_tiles = 3 * l.NP / 128;
-  int ns = 148 / m_tiles;
+  const int tiles = (3 * l.NP / 128) * (l.NP > 512 ? l.NP / 512 : 1);
+  int ns = 148 / tiles;
   const long long K = (long long)T * l.BP;
   while (ns > 1 && K / ns < 256) --ns;
   return ns < 1 ? 1 : ns;

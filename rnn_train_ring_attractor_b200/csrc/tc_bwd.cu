@@ -41,9 +41,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     if (warp == 0 && lane == 0) {
       producer_loop<NP, PAIR>(c, &tmW, total_steps, 302);
     } else if (warp == 1 && lane == 0) {
-      if (c.leader) mma_loop<NP, PAIR, false>(c, total_steps, T, 310);
+      if (c.leader) mma_loop<NP, PAIR, false>(c, total_steps, T, 310, true);
     } else if (warp == 2 && lane == 0) {
-      relay_loop<NP, PAIR, false>(c, total_steps, T, 320, [](int) {});
+      relay_loop<NP, PAIR, false>(c, total_steps, T, 320, [](int, int) {});
     }
   } else {
     reg_inc<232>();
@@ -56,8 +56,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     const float J0 = p.J0, J1 = p.J1, alpha = p.alpha, beta = 1.f - p.alpha;
     const bool has_coef = p.coef_x != nullptr;
     const bool want_dA = p.dA_part != nullptr;
+    const int rq = (2 * q) / C_::SLOTS;  // the K round this CTA's own chunks belong to
+    FreePhases<NP, PAIR> freed;
     uint32_t g = 0;
-    for (int tile = cluster_id; tile < p.n_tiles; tile += n_clusters) {
+    bool stop = false;  // a wait of this CTA was abandoned (the status word says which): same value in all 256 threads
+    for (int tile = cluster_id; tile < p.n_tiles && !stop; tile += n_clusters) {
       const int b = tile * C_::TILE_ROWS + c.half * 128 + row;
       const bool valid = b < p.B;
       float master[64];  // carry on entry of `produce`, g_t afterwards
@@ -147,8 +150,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           }
         }
         // delta_t: A operand of this step everywhere, and column block 0 of DL row block t (TMA store from the chunks)
-        publish_chunks<NP, PAIR>(c, packed, row, h, warp, lane, &tmDL, q * 128,
-                                 t * p.BP + tile * C_::TILE_ROWS + c.half * 128);
+        stop = publish_chunks<NP, PAIR>(c, packed, row, h, warp, lane, &tmDL, q * 128,
+                                        t * p.BP + tile * C_::TILE_ROWS + c.half * 128);
+        if (stop) return;
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 12);
         // off the critical path: [delta | L*delta | R*delta] for the weight-gradient GEMM.  The scaled copies are
         // formed from the bf16 delta the MMA sees, so the three blocks are consistent with one another.
@@ -174,7 +178,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       };
 
       prefetch(T - 1);
+      freed.before_publish(c, g, rq, 308);
       produce(T - 1);
+      if (stop) break;
       for (int t = T - 1; t >= 0; --t, ++g) {
         if (t > 0) prefetch(t - 1);
         float c0 = 0.f, dAl = 0.f, dAr = 0.f;
@@ -184,6 +190,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           if (warp == 4 && lane == 0) RINGRNN_STAMP(g, s == 0 ? 5 : 7);
           tcgen05_fence_after();
           if (s == 0) {
+            freed.early(c, g, 308);
             uint32_t sraw;
             tmem_ld1(tmem_base + lane_base + SUM_COL, &sraw);  // sum_i delta_t[b,i]
             tmem_ld_wait();
@@ -228,10 +235,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           dp[(size_t)T * p.BP] = dAr;
         }
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 9);
-        mbar_wait<true>(bars + OFF_ALL_FREE, g & 1u, wctx, 308);
+        if (t > 0) freed.before_publish(c, g + 1, rq, 308);
+        else freed.end_of_step(c, g, 308);
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 10);
         if (t > 0) {
           produce(t - 1);
+          if (stop) break;
           if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 11);
         } else if (p.grad_r_init != nullptr && valid) {
 #pragma unroll
@@ -278,6 +287,7 @@ int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const CUtensor
   if (NP == 128) return pair ? launch_bwd_tc<128, true>(tmW, tmDL, p, s) : launch_bwd_tc<128, false>(tmW, tmDL, p, s);
   if (NP == 256) return pair ? launch_bwd_tc<256, true>(tmW, tmDL, p, s) : launch_bwd_tc<256, false>(tmW, tmDL, p, s);
   if (NP == 512) return pair ? launch_bwd_tc<512, true>(tmW, tmDL, p, s) : launch_bwd_tc<512, false>(tmW, tmDL, p, s);
+  if (NP == 1024 && !pair) return launch_bwd_tc<1024, false>(tmW, tmDL, p, s);  // two K rounds per step, clusters of 8
   return RINGRNN_ERR_UNSUPPORTED;
 }
 

@@ -22,7 +22,6 @@ template <int ACT, int NP, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmR0, const TcFwdParams p) {
   using C_ = Cfg<NP, PAIR>;
-  constexpr int KC = C_::KC;
   extern __shared__ uint8_t smem_raw[];
   const Ctx<NP, PAIR> c = setup_cta<NP, PAIR>(smem_raw, p.dec_u, p.dec_v, p.N, p.status);
   const uint32_t a_base = c.a_base, bars = c.bars, tmem_base = c.tmem_base;
@@ -40,16 +39,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     if (warp == 0 && lane == 0) {
       producer_loop<NP, PAIR>(c, &tmW, total_steps, 202);
     } else if (warp == 1 && lane == 0) {
-      if (c.leader) mma_loop<NP, PAIR, true>(c, total_steps, T, 210);
+      if (c.leader) mma_loop<NP, PAIR, true>(c, total_steps, T, 210, p.Rh != nullptr);
     } else if (warp == 2 && lane == 0) {
       tma_prefetch_desc(&tmR0);
-      relay_loop<NP, PAIR, true>(c, total_steps, T, 220, [&](int it) {
-        // initial state of the tile: this CTA's 128 samples, all K chunks (the previous tile's MMAs are done:
-        // the relay has seen every phase of mma_done)
+      relay_loop<NP, PAIR, true>(c, total_steps, T, 220, [&](int it, int round) {
+        // initial state of the tile: this CTA's 128 samples, the K chunks of this round (the MMAs that read the
+        // slots before are done: the relay has seen every phase of mma_done)
         const int tile = cluster_id + it * n_clusters;
-        for (int kc = 0; kc < KC; ++kc) {
-          mbar_arrive_expect_tx(bars + OFF_A_FULL + 8 * kc, CHUNK_BYTES);
-          tma_load_2d(a_base + kc * CHUNK_BYTES, &tmR0, bars + OFF_A_FULL + 8 * kc, kc * 64,
+        for (int slot = 0; slot < C_::SLOTS; ++slot) {
+          mbar_arrive_expect_tx(bars + OFF_A_FULL + 8 * slot, CHUNK_BYTES);
+          tma_load_2d(a_base + slot * CHUNK_BYTES, &tmR0, bars + OFF_A_FULL + 8 * slot, (round * C_::SLOTS + slot) * 64,
                       tile * C_::TILE_ROWS + c.half * 128);
         }
       });
@@ -67,8 +66,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     const int slot = 2 * q + h;
     const float J0 = p.J0, J1 = p.J1, alpha = p.alpha, beta = 1.f - p.alpha;
     const bool want_dec = p.dec_part != nullptr;
+    const int rq = (2 * q) / C_::SLOTS;  // the K round this CTA's own chunks belong to
+    FreePhases<NP, PAIR> freed;
     uint32_t g = 0;
-    for (int tile = cluster_id; tile < p.n_tiles; tile += n_clusters) {
+    bool stop = false;  // a wait of this CTA was abandoned (the status word says which): same value in all 256 threads
+    for (int tile = cluster_id; tile < p.n_tiles && !stop; tile += n_clusters) {
       const int b = tile * C_::TILE_ROWS + c.half * 128 + row;
       const bool valid = b < p.B;
       float master[64];
@@ -93,6 +95,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           mbar_wait(bars + OFF_D_FULL + 8 * s, g & 1u, wctx, 207);
           if (warp == 4 && lane == 0) RINGRNN_STAMP(g, s == 0 ? 5 : 7);
           tcgen05_fence_after();
+          if (s == 0) freed.early(c, g, 208);
+          // Last step of a tile: nothing is published, and the next tile's first operand comes by TMA, so its MMAs
+          // wait for nothing but this accumulator.  The step's "free" phases must be consumed BEFORE the accumulator
+          // is handed back, or the barrier could complete another phase first and the parity wait below would
+          // never return.  (They complete together with this accumulator, give or take the skew between the CTAs.)
+          if (s == 1 && t + 1 == T) freed.end_of_step(c, g, 208);
           uint32_t yo[32], yl[32], yr[32];
           const uint32_t col = tmem_base + lane_base + s * 256 + 32 * h;
           if (s == 0) {
@@ -151,15 +159,19 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             sg[p.BP] = neg;
           }
         }
-        // every CTA of the cluster has finished reading r_{t-1} (waited for in every step so that no phase of
-        // the barrier is skipped); then publish r_t
+        // every CTA of the cluster has finished reading what the slots of this CTA's chunks held (every phase of
+        // the barriers is waited for, published or not, so that none is skipped); then publish r_t:
+        // it becomes the A operand of step t+1 everywhere and, in training, row block t+1 of the saved state
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 9);
-        mbar_wait<true>(bars + OFF_ALL_FREE, g & 1u, wctx, 208);
-        if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 10);
-        // r_t becomes the A operand of step t+1 everywhere and, in training, row block t+1 of the saved state
-        if (t + 1 < T)
-          publish_chunks<NP, PAIR>(c, packed, row, h, warp, lane, p.Rh != nullptr ? &tmR0 : nullptr, q * 128,
-                                   (t + 1) * p.BP + tile * C_::TILE_ROWS + c.half * 128);
+        if (t + 1 < T) {
+          freed.before_publish(c, g + 1, rq, 208);
+          if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 10);
+          stop = publish_chunks<NP, PAIR>(c, packed, row, h, warp, lane, p.Rh != nullptr ? &tmR0 : nullptr, q * 128,
+                                          (t + 1) * p.BP + tile * C_::TILE_ROWS + c.half * 128);
+          if (stop) break;
+        } else {
+          freed.end_of_step(c, g, 208);
+        }
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 11);
         // off the critical path: fp32 history, decode sums
         if (p.hist != nullptr && valid) {
@@ -186,6 +198,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           dp[(size_t)2 * T * p.BP] = pa;
         }
       }
+      if (stop) break;
       if (p.final_state != nullptr && valid) {
 #pragma unroll
         for (int s = 0; s < 2; ++s)
@@ -235,6 +248,12 @@ int tc_forward_launch(int act, int NP, bool pair, const CUtensorMap& tmW, const 
   RINGRNN_TCF(RINGRNN_ACT_TANH, 128) RINGRNN_TCF(RINGRNN_ACT_TANH, 256) RINGRNN_TCF(RINGRNN_ACT_TANH, 512)
   RINGRNN_TCF(RINGRNN_ACT_SILU, 128) RINGRNN_TCF(RINGRNN_ACT_SILU, 256) RINGRNN_TCF(RINGRNN_ACT_SILU, 512)
 #undef RINGRNN_TCF
+  if (NP == 1024 && !pair) {  // two K rounds per step, clusters of 8
+    if (act == RINGRNN_ACT_RELU) return launch_fwd_tc<RINGRNN_ACT_RELU, 1024, false>(tmW, tmR0, p, s);
+    if (act == RINGRNN_ACT_GELU) return launch_fwd_tc<RINGRNN_ACT_GELU, 1024, false>(tmW, tmR0, p, s);
+    if (act == RINGRNN_ACT_TANH) return launch_fwd_tc<RINGRNN_ACT_TANH, 1024, false>(tmW, tmR0, p, s);
+    if (act == RINGRNN_ACT_SILU) return launch_fwd_tc<RINGRNN_ACT_SILU, 1024, false>(tmW, tmR0, p, s);
+  }
   return RINGRNN_ERR_UNSUPPORTED;
 }
 

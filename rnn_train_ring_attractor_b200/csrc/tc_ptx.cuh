@@ -129,6 +129,19 @@ __device__ __forceinline__ void tcgen05_fence_after() {
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+// named barrier that also returns the OR of `pred` over its participants: a decision every thread sees alike
+__device__ __forceinline__ bool named_bar_or(uint32_t id, uint32_t threads, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "bar.red.or.pred q, %2, %3, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)pred), "r"(id), "r"(threads)
+      : "memory");
+  return r != 0;
+}
 
 // ---- cluster --------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {

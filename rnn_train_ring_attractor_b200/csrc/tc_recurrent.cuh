@@ -1,6 +1,6 @@
 // Shared definitions of the bf16 tensor-core recurrent kernels (forward and reverse-time).
 //
-// Decomposition.  The padded neuron count NP (128, 256 or 512) is split into C = NP/128 slices of 128 neurons.
+// Decomposition.  The padded neuron count NP (128, 256, 512 or 1024) is split into C = NP/128 slices of 128 neurons.
 // A thread-block cluster owns one tile of samples at a time and runs all its timesteps; the CTA that owns
 // slice q produces neurons [128q, 128q+128) in two sub-slices of 64.  Per step a CTA needs the whole previous
 // state of its 128 samples as the A operand [128 x NP] (bf16, K-major, 128-byte swizzle, one 16 KB chunk per
@@ -8,6 +8,11 @@
 // shared-memory stages (or loaded once when they fit).  After the epilogue each CTA pushes its two new
 // 64-neuron chunks into the A buffers of the CTAs that hold the same samples, with one-destination bulk copies
 // over distributed shared memory; mbarriers carry the byte counts.
+//
+// K rounds.  The A buffer has at most 8 chunk slots (128 KB).  For NP = 1024 (16 chunks) a step therefore runs in
+// two rounds: round 0 multiplies chunks 0-7 (published by slices 0-3) into the accumulators, then, once every CTA of
+// the cluster is done with them, slices 4-7 publish chunks 8-15 into the same slots and round 1 accumulates on top.
+// Chunk kc lives in slot kc % 8 and is used in round kc / 8; NP <= 512 has a single round.
 //
 // Two cluster shapes:
 //   single (PAIR = false): C CTAs, 128 samples, each CTA issues its own tcgen05.mma (M = 128, N = 208).
@@ -110,10 +115,12 @@ struct Cfg {
   static constexpr int CL = PAIR ? 2 * C : C;    // CTAs per cluster
   static constexpr int TILE_ROWS = PAIR ? 256 : 128;
   static constexpr int KC = NP / 64;             // K chunks
+  static constexpr int SLOTS = KC < 8 ? KC : 8;  // chunk slots of the A buffer
+  static constexpr int ROUNDS = KC / SLOTS;      // K rounds per step
   static constexpr int RB = block_rows(PAIR);    // rows of one weight block = accumulator columns used
   static constexpr int WROWS = PAIR ? RB / 2 : RB;  // rows of a weight tile this CTA loads
   static constexpr int WT_BYTES = WROWS * 128;   // one [WROWS x 64] bf16 tile
-  static constexpr int A_BYTES = KC * CHUNK_BYTES;
+  static constexpr int A_BYTES = SLOTS * CHUNK_BYTES;
   static constexpr int TILES = 2 * KC;           // weight tiles per step
   static constexpr int AUX = 2048;               // barriers, flags, decode vectors
   static constexpr int STAGE_BYTES = 8 * 2048;   // one 32-row x 64-byte transposition buffer per epilogue warp
@@ -124,19 +131,23 @@ struct Cfg {
   static_assert(NS >= 2, "weight ring too small");
   static_assert(NS <= 16, "barrier block sized for 16 stages");
   static_assert(WT_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
+  static_assert(!PAIR || ROUNDS == 1, "CTA pairs are written for a single K round");
+  static_assert(!RESIDENT || ROUNDS == 1, "resident weights are written for a single K round");
+  static_assert(ROUNDS <= 2, "barrier block sized for two K rounds");
 };
 
 // barrier block: byte offsets from its base
 constexpr uint32_t OFF_W_FULL = 0;     // [16]
 constexpr uint32_t OFF_W_EMPTY = 128;  // [16]
-constexpr uint32_t OFF_A_FULL = 256;   // [8]  chunk kc of this CTA's A buffer is complete
+constexpr uint32_t OFF_A_FULL = 256;   // [8]  slot i of this CTA's A buffer holds its chunk of the current round
 constexpr uint32_t OFF_D_FULL = 320;   // [2]
 constexpr uint32_t OFF_D_EMPTY = 336;  // [2]
-constexpr uint32_t OFF_MMA_DONE = 352;
-constexpr uint32_t OFF_ALL_FREE = 360;
-constexpr uint32_t OFF_TMEM_SLOT = 368;
-constexpr uint32_t OFF_DEAD = 372;
+constexpr uint32_t OFF_MMA_DONE = 352; // one phase per (step, round): this CTA's MMAs of the round are complete
+constexpr uint32_t OFF_ALL_FREE = 360; // [2]  per round, one phase per step: every CTA's MMAs of the round are complete
+constexpr uint32_t OFF_TMEM_SLOT = 376;
+constexpr uint32_t OFF_DEAD = 380;
 constexpr uint32_t OFF_A_PAIR = 384;   // [8]  (even CTA of a pair) chunk kc is complete in the odd CTA too
+constexpr uint32_t OFF_STORE_DONE = 448;  // (two rounds) the TMA store of this CTA's own chunks has read them
 constexpr uint32_t OFF_UV = 512;       // float u[128], v[128]
 
 template <int REGS>
@@ -266,6 +277,8 @@ __device__ __forceinline__ Ctx<NP, PAIR> setup_cta(uint8_t* smem_raw, const floa
     mbar_init(c.bars + OFF_D_EMPTY + 8, PAIR ? 16 : 8);
     mbar_init(c.bars + OFF_MMA_DONE, 1);
     mbar_init(c.bars + OFF_ALL_FREE, C_::C);
+    mbar_init(c.bars + OFF_ALL_FREE + 8, C_::C);
+    mbar_init(c.bars + OFF_STORE_DONE, 1);
     fence_mbar_init();
   }
   if (threadIdx.x < 256) {
@@ -291,6 +304,9 @@ __device__ __forceinline__ Ctx<NP, PAIR> setup_cta(uint8_t* smem_raw, const floa
 template <int NP, bool PAIR>
 __device__ __forceinline__ void teardown_cta(const Ctx<NP, PAIR>& c) {
   using namespace tc;
+  // abandoned run: the roles stopped wherever they were, so tensor-core work and copies may still be in flight with
+  // nobody left to wait for their barriers; give them time to land before the accumulator memory is handed back
+  if (*c.wctx.dead) __nanosleep(200000);
   // nobody leaves while a peer may still signal or copy into this CTA
   tcgen05_fence_before();
   __syncthreads();
@@ -304,16 +320,18 @@ __device__ __forceinline__ void teardown_cta(const Ctx<NP, PAIR>& c) {
   }
 }
 
-// Weight stream (one thread per CTA).  Tile order per step: sub-slice 0 then 1, K chunks starting at this slice's own.
+// Weight stream (one thread per CTA).  Tile order per step: round by round, sub-slice 0 then 1, the slots starting at
+// this slice's own.
 template <int NP, bool PAIR>
 __device__ __forceinline__ void producer_loop(const Ctx<NP, PAIR>& c, const CUtensorMap* tmW, uint32_t total_steps,
                                               int code) {
   using C_ = Cfg<NP, PAIR>;
   using namespace tc;
-  constexpr int KC = C_::KC, NS = C_::NS;
+  constexpr int KC = C_::KC, NS = C_::NS, SL = C_::SLOTS, R = C_::ROUNDS;
   tma_prefetch_desc(tmW);
   if (total_steps == 0) return;
   const uint64_t keep = l2_policy_evict_last();
+  const int rot = (2 * c.q) % SL;
   auto issue = [&](int st, int s, int kc) {
     const uint32_t bar = c.bars + OFF_W_FULL + 8 * st;
     const int y = (c.q * 2 + s) * C_::RB + c.half * C_::WROWS;
@@ -323,37 +341,39 @@ __device__ __forceinline__ void producer_loop(const Ctx<NP, PAIR>& c, const CUte
   };
   if (C_::RESIDENT) {
     for (int s = 0; s < 2; ++s)
-      for (int i = 0; i < KC; ++i) issue(s * KC + i, s, (2 * c.q + i) % KC);
+      for (int i = 0; i < KC; ++i) issue(s * KC + i, s, (rot + i) % SL);
   } else {
     uint32_t wcount = 0;
     for (uint32_t g = 0; g < total_steps; ++g)
-      for (int s = 0; s < 2; ++s)
-        for (int i = 0; i < KC; ++i, ++wcount) {
-          const int st = wcount % NS;
-          if (wcount >= (uint32_t)NS) mbar_wait(c.bars + OFF_W_EMPTY + 8 * st, (wcount / NS - 1) & 1u, c.wctx, code);
-          issue(st, s, (2 * c.q + i) % KC);
-        }
+      for (int round = 0; round < R; ++round)
+        for (int s = 0; s < 2; ++s)
+          for (int i = 0; i < SL; ++i, ++wcount) {
+            const int st = wcount % NS;
+            if (wcount >= (uint32_t)NS &&
+                !mbar_wait(c.bars + OFF_W_EMPTY + 8 * st, (wcount / NS - 1) & 1u, c.wctx, code))
+              return;  // abandoned: issue nothing more
+            issue(st, s, round * SL + (rot + i) % SL);
+          }
   }
 }
 
-// Should the byte count of the copy that will bring chunk kc for step g+1 be armed after step g's wait?
-// Forward: the first step of every tile is loaded by TMA instead (armed there); reverse: every step but the last.
-template <bool FWD>
-__device__ __forceinline__ bool arm_next(uint32_t g, uint32_t total_steps, int T) {
-  return FWD ? ((int)(g % (uint32_t)T) + 1 < T) : (g + 1 < total_steps);
-}
-
-// MMA issuer (one thread of the leader CTA).
+// Every role leaves its loop at the first abandoned wait (a wait that ran out sets the CTA's `dead` flag and the
+// global status word): nothing more is issued, and the CTA drains through teardown_cta.
+//
+// MMA issuer (one thread of the leader CTA).  `stores`: the epilogue publishes this CTA's chunks with a TMA store
+// (only looked at with two K rounds, where a peer overwrites the slots of this CTA's own chunks in the other round).
 template <int NP, bool PAIR, bool FWD>
-__device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_steps, int T, int code) {
+__device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_steps, int T, int code, bool stores) {
   using C_ = Cfg<NP, PAIR>;
   using namespace tc;
-  constexpr int KC = C_::KC, NS = C_::NS;
+  constexpr int KC = C_::KC, NS = C_::NS, SL = C_::SLOTS, R = C_::ROUNDS;
   constexpr uint32_t idesc = make_idesc_bf16(PAIR ? 256 : 128, C_::RB, 0, 0);
-  uint32_t wcount = 0;
+  const int rot = (2 * c.q) % SL, rq = (2 * c.q) / SL;
+  uint32_t wcount = 0, ph = 0, npub = 0;
+  int t = 0;  // step within the tile
   if (!FWD && total_steps > 0)  // reverse: nothing loads the first A operand by TMA, peers push it
-    for (int kc = 0; kc < KC; ++kc)
-      if ((kc >> 1) != c.q) mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * kc, CHUNK_BYTES);
+    for (int slot = 0; slot < SL; ++slot)
+      if ((slot >> 1) != c.q) mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * slot, CHUNK_BYTES);
   auto commit = [&](uint32_t bar) {
     if (PAIR) umma_commit_pair(bar, c.pair_mask);
     else umma_commit(bar);
@@ -362,64 +382,85 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
 #ifdef RINGRNN_TIMELINE
     long long acc_w = 0, acc_a = 0, acc_p = 0, t0;
 #endif
-    for (int s = 0; s < 2; ++s) {
-      if (g > 0) mbar_wait<PAIR>(c.bars + OFF_D_EMPTY + 8 * s, (g - 1) & 1u, c.wctx, code + 0);
-      RINGRNN_STAMP(g, s == 0 ? 0 : 2);
-      tcgen05_fence_after();
-      for (int i = 0; i < KC; ++i) {
-        const int kc = (2 * c.q + i) % KC;
-        if (s == 0) {
-#ifdef RINGRNN_TIMELINE
-          t0 = clock64();
-#endif
-          mbar_wait(c.bars + OFF_A_FULL + 8 * kc, g & 1u, c.wctx, code + 1);
-#ifdef RINGRNN_TIMELINE
-          acc_a += clock64() - t0;
-          t0 = clock64();
-#endif
-          // chunks owned by other slices arrive as bulk copies: arm the byte count of the next step's copy
-          if ((kc >> 1) != c.q && arm_next<FWD>(g, total_steps, T))
-            mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * kc, CHUNK_BYTES);
-          if (PAIR) mbar_wait<true>(c.bars + OFF_A_PAIR + 8 * kc, g & 1u, c.wctx, code + 2);
-#ifdef RINGRNN_TIMELINE
-          acc_p += clock64() - t0;
-          if (i == 1) RINGRNN_STAMP(g, 1);
-#endif
-        }
-        int st;
-        if (C_::RESIDENT) {
-          st = s * KC + i;
-          if (g == 0) mbar_wait(c.bars + OFF_W_FULL + 8 * st, 0, c.wctx, code + 3);
-        } else {
-          st = wcount % NS;
-#ifdef RINGRNN_TIMELINE
-          t0 = clock64();
-#endif
-          mbar_wait(c.bars + OFF_W_FULL + 8 * st, (wcount / NS) & 1u, c.wctx, code + 3);
-#ifdef RINGRNN_TIMELINE
-          acc_w += clock64() - t0;
-#endif
+#pragma unroll
+    for (int round = 0; round < R; ++round, ++ph) {
+      // Will the chunks of the next phase arrive as bulk copies from peers (then their byte counts are armed here,
+      // right after this phase's wait)?  Forward: the first step of every tile is loaded by TMA instead (armed
+      // there); reverse: every phase but the last.
+      const int next_round = (round + 1) % R;
+      const int next_t = (round + 1 < R) ? t : (t + 1 == T ? 0 : t + 1);
+      const bool next_by_copy = FWD ? (next_t != 0) : (ph + 1 < total_steps * (uint32_t)R);
+      for (int s = 0; s < 2; ++s) {
+        if (round == 0) {
+          if (g > 0 && !mbar_wait<PAIR>(c.bars + OFF_D_EMPTY + 8 * s, (g - 1) & 1u, c.wctx, code + 0)) return;
+          RINGRNN_STAMP(g, s == 0 ? 0 : 2);
         }
         tcgen05_fence_after();
-        const uint32_t a_lo = desc_lo(c.a_base + kc * CHUNK_BYTES, 16), b_lo = desc_lo(c.w_base + st * C_::WT_BYTES, 16);
+        for (int i = 0; i < SL; ++i) {
+          const int slot = (rot + i) % SL;
+          if (s == 0) {
+#ifdef RINGRNN_TIMELINE
+            t0 = clock64();
+#endif
+            if (!mbar_wait(c.bars + OFF_A_FULL + 8 * slot, ph & 1u, c.wctx, code + 1)) return;
+#ifdef RINGRNN_TIMELINE
+            acc_a += clock64() - t0;
+            t0 = clock64();
+#endif
+            if (next_by_copy && ((next_round * SL + slot) >> 1) != c.q)
+              mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * slot, CHUNK_BYTES);
+            if (PAIR && !mbar_wait<true>(c.bars + OFF_A_PAIR + 8 * slot, g & 1u, c.wctx, code + 2)) return;
+#ifdef RINGRNN_TIMELINE
+            acc_p += clock64() - t0;
+            if (i == 1 && round == 0) RINGRNN_STAMP(g, 1);
+#endif
+          }
+          int st;
+          if (C_::RESIDENT) {
+            st = s * KC + i;
+            if (g == 0 && !mbar_wait(c.bars + OFF_W_FULL + 8 * st, 0, c.wctx, code + 3)) return;
+          } else {
+            st = wcount % NS;
+#ifdef RINGRNN_TIMELINE
+            t0 = clock64();
+#endif
+            if (!mbar_wait(c.bars + OFF_W_FULL + 8 * st, (wcount / NS) & 1u, c.wctx, code + 3)) return;
+#ifdef RINGRNN_TIMELINE
+            acc_w += clock64() - t0;
+#endif
+          }
+          tcgen05_fence_after();
+          const uint32_t a_lo = desc_lo(c.a_base + slot * CHUNK_BYTES, 16), b_lo = desc_lo(c.w_base + st * C_::WT_BYTES, 16);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          if (PAIR) umma_ss_pair_lo(c.tmem_base + s * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc, (i > 0 || ks > 0) ? 1u : 0u);
-          else umma_ss_lo(c.tmem_base + s * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc, (i > 0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint32_t acc = (round > 0 || i > 0 || ks > 0) ? 1u : 0u;
+            if (PAIR) umma_ss_pair_lo(c.tmem_base + s * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc, acc);
+            else umma_ss_lo(c.tmem_base + s * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc, acc);
+          }
+          if (!C_::RESIDENT) {
+            commit(c.bars + OFF_W_EMPTY + 8 * st);
+            ++wcount;
+          }
         }
-        if (!C_::RESIDENT) {
-          commit(c.bars + OFF_W_EMPTY + 8 * st);
-          ++wcount;
+        if (round == R - 1) {
+          commit(c.bars + OFF_D_FULL + 8 * s);
+          RINGRNN_STAMP(g, s == 0 ? 3 : 4);
         }
       }
-      commit(c.bars + OFF_D_FULL + 8 * s);
-      RINGRNN_STAMP(g, s == 0 ? 3 : 4);
+      if (R > 1 && round == rq && stores && (!FWD || t != 0)) {
+        // this CTA's own chunks sit in slots a peer fills in the next phase: the TMA store that also reads them
+        // must be through before "free" goes out
+        if (!mbar_wait(c.bars + OFF_STORE_DONE, npub & 1u, c.wctx, code + 4)) return;
+        ++npub;
+      }
+      commit(c.bars + OFF_MMA_DONE);
+      // "this MMA unit no longer reads the A buffer of this round", straight to every CTA of the cluster
+      const uint32_t free_bar = c.bars + OFF_ALL_FREE + 8 * round;
+      if (PAIR) umma_commit_pair(free_bar, (uint16_t)((1u << C_::CL) - 1u));
+      else if (C_::CL > 1) umma_commit_fanout(free_bar, (uint16_t)((1u << C_::CL) - 1u));
+      else umma_commit(free_bar);
     }
-    commit(c.bars + OFF_MMA_DONE);
-    // "this MMA unit no longer reads the A buffers of step g", straight to every CTA of the cluster
-    if (PAIR) umma_commit_pair(c.bars + OFF_ALL_FREE, (uint16_t)((1u << C_::CL) - 1u));
-    else if (C_::CL > 1) umma_commit_fanout(c.bars + OFF_ALL_FREE, (uint16_t)((1u << C_::CL) - 1u));
-    else umma_commit(c.bars + OFF_ALL_FREE);
+    t = (t + 1 == T) ? 0 : t + 1;
 #ifdef RINGRNN_TIMELINE
     RINGRNN_STAMP_VAL(g, 13, acc_w);
     RINGRNN_STAMP_VAL(g, 14, acc_a);
@@ -428,33 +469,76 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
   }
 }
 
-// Relay (one thread per CTA): follows every phase of mma_done, so it knows when the A buffer may take the next tile:
-// `tile_start(tile_index)` runs before the first step of each tile (forward: TMA load of the initial state into this
-// CTA's A buffer).  The odd CTA of a pair also forwards "chunk kc is complete here" to its leader and arms its own
-// incoming copies.
+// Relay (one thread per CTA): follows every phase of mma_done, so it knows when the A buffer may take new contents:
+// `tile_start(tile_index, round)` runs before each round of the first step of each tile (forward: TMA load of that
+// round's chunks of the initial state into this CTA's A buffer).  The odd CTA of a pair also forwards "chunk kc is
+// complete here" to its leader and arms its own incoming copies.
 template <int NP, bool PAIR, bool FWD, class TileStart>
 __device__ __forceinline__ void relay_loop(const Ctx<NP, PAIR>& c, uint32_t total_steps, int T, int code,
                                            TileStart tile_start) {
   using C_ = Cfg<NP, PAIR>;
   using namespace tc;
-  constexpr int KC = C_::KC;
+  constexpr int KC = C_::KC, R = C_::ROUNDS;
   if (PAIR && !c.leader && !FWD && total_steps > 0)
     for (int kc = 0; kc < KC; ++kc)
       if ((kc >> 1) != c.q) mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * kc, CHUNK_BYTES);
+  uint32_t ph = 0;
+  int t = 0, it = 0;
   for (uint32_t g = 0; g < total_steps; ++g) {
-    if (g % (uint32_t)T == 0) tile_start((int)(g / (uint32_t)T));
-    if (PAIR && !c.leader) {
-      for (int i = 0; i < KC; ++i) {
-        const int kc = (2 * c.q + i) % KC;
-        mbar_wait(c.bars + OFF_A_FULL + 8 * kc, g & 1u, c.wctx, code + 0);
-        if ((kc >> 1) != c.q && arm_next<FWD>(g, total_steps, T))
-          mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * kc, CHUNK_BYTES);
-        mbar_arrive_cluster(c.bars + OFF_A_PAIR + 8 * kc, c.leader_rank);
+    for (int round = 0; round < R; ++round, ++ph) {
+      if (t == 0) tile_start(it, round);
+      if (PAIR && !c.leader) {
+        const bool next_by_copy = FWD ? (t + 1 < T) : (g + 1 < total_steps);
+        for (int i = 0; i < KC; ++i) {
+          const int kc = (2 * c.q + i) % KC;
+          if (!mbar_wait(c.bars + OFF_A_FULL + 8 * kc, g & 1u, c.wctx, code + 0)) return;
+          if ((kc >> 1) != c.q && next_by_copy) mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * kc, CHUNK_BYTES);
+          mbar_arrive_cluster(c.bars + OFF_A_PAIR + 8 * kc, c.leader_rank);
+        }
       }
+      if (!mbar_wait(c.bars + OFF_MMA_DONE, ph & 1u, c.wctx, code + 1)) return;
     }
-    mbar_wait(c.bars + OFF_MMA_DONE, g & 1u, c.wctx, code + 1);
+    if (++t == T) {
+      t = 0;
+      ++it;
+    }
   }
 }
+
+// Which phases of the per-round "free" barriers an epilogue thread has consumed.  Every thread consumes every phase
+// of every round's barrier, in order and never twice (a parity wait on a barrier that has moved on by two phases
+// would never return).
+template <int NP, bool PAIR>
+struct FreePhases {
+  static constexpr int R = Cfg<NP, PAIR>::ROUNDS;
+  uint32_t cnt[R];
+  __device__ __forceinline__ FreePhases() {
+#pragma unroll
+    for (int r = 0; r < R; ++r) cnt[r] = 0;
+  }
+  __device__ __forceinline__ void upto(const Ctx<NP, PAIR>& c, int r, uint32_t n, int code) {
+    while (cnt[r] < n) {
+      tc::mbar_wait<true>(c.bars + OFF_ALL_FREE + 8 * r, cnt[r] & 1u, c.wctx, code);
+      ++cnt[r];
+    }
+  }
+  // Once an accumulator of step g is complete, every round of step g but the last is over in the whole cluster
+  // (the chunks of a round are only published after the previous round's "free").
+  __device__ __forceinline__ void early(const Ctx<NP, PAIR>& c, uint32_t g, int code) {
+#pragma unroll
+    for (int r = 0; r + 1 < R; ++r) upto(c, r, g + 1, code);
+  }
+  // all rounds of steps <= g
+  __device__ __forceinline__ void end_of_step(const Ctx<NP, PAIR>& c, uint32_t g, int code) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) upto(c, r, g + 1, code);
+  }
+  // everything that precedes round rq of step gt: the slots of this CTA's own chunks may be rewritten
+  __device__ __forceinline__ void before_publish(const Ctx<NP, PAIR>& c, uint32_t gt, int rq, int code) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) upto(c, r, gt + (r < rq ? 1u : 0u), code);
+  }
+};
 
 // Epilogue helpers ------------------------------------------------------------------------------------------------
 // "this warp has read accumulator s of step g": to the leader's barrier (remote for the odd CTA of a pair)
@@ -474,9 +558,10 @@ __device__ __forceinline__ void release_accumulator(const Ctx<NP, PAIR>& c, int 
 // same samples for the other slices and, if `tm_store` is given, stores them with TMA to rows [y, y+128),
 // columns [x0, x0+128) of a row-major bf16 tensor (the saved state, or delta for the weight-gradient GEMM): the
 // chunks are already in the layout a 128-byte-swizzled TMA box expects, so this costs no load/store instructions.
-// All 256 epilogue threads must call it.
+// All 256 epilogue threads must call it.  Returns true, to all of them alike, if a wait of this CTA was abandoned
+// (nothing is copied then): the one place where the epilogue threads may leave their loops together.
 template <int NP, bool PAIR>
-__device__ __forceinline__ void publish_chunks(const Ctx<NP, PAIR>& c, const uint32_t* packed, int row, int h, int warp,
+__device__ __forceinline__ bool publish_chunks(const Ctx<NP, PAIR>& c, const uint32_t* packed, int row, int h, int warp,
                                                int lane, const CUtensorMap* tm_store, int x0, int y) {
   using C_ = Cfg<NP, PAIR>;
   using namespace tc;
@@ -487,7 +572,7 @@ __device__ __forceinline__ void publish_chunks(const Ctx<NP, PAIR>& c, const uin
   }
 #pragma unroll
   for (int s = 0; s < 2; ++s) {
-    const uint32_t tile_addr = c.a_base + (2 * c.q + s) * CHUNK_BYTES;
+    const uint32_t tile_addr = c.a_base + ((2 * c.q + s) % C_::SLOTS) * CHUNK_BYTES;
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
       const uint32_t unit = (uint32_t)(4 * h + v);
@@ -498,22 +583,28 @@ __device__ __forceinline__ void publish_chunks(const Ctx<NP, PAIR>& c, const uin
     }
   }
   fence_proxy_async_smem();
-  named_bar_sync(1, 256);
-  if (warp == 4 && lane == 0) {
+  const bool stop = named_bar_or(1, 256, *c.wctx.dead != 0);
+  if (warp == 4 && lane == 0 && !stop) {
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
-      const int kc = 2 * c.q + s;
-      const uint32_t tile_addr = c.a_base + kc * CHUNK_BYTES;
-      mbar_arrive(c.bars + OFF_A_FULL + 8 * kc);
+      const int slot = (2 * c.q + s) % C_::SLOTS;
+      const uint32_t tile_addr = c.a_base + slot * CHUNK_BYTES;
+      mbar_arrive(c.bars + OFF_A_FULL + 8 * slot);
       for (int q2 = 0; q2 < C_::C; ++q2)
-        if (q2 != c.q) dsmem_bulk_copy(tile_addr, tile_addr, CHUNK_BYTES, c.bars + OFF_A_FULL + 8 * kc, c.peer_rank(q2));
+        if (q2 != c.q) dsmem_bulk_copy(tile_addr, tile_addr, CHUNK_BYTES, c.bars + OFF_A_FULL + 8 * slot, c.peer_rank(q2));
     }
     if (tm_store != nullptr) {
 #pragma unroll
-      for (int s = 0; s < 2; ++s) tma_store_2d(tm_store, c.a_base + (2 * c.q + s) * CHUNK_BYTES, x0 + 64 * s, y);
+      for (int s = 0; s < 2; ++s)
+        tma_store_2d(tm_store, c.a_base + ((2 * c.q + s) % C_::SLOTS) * CHUNK_BYTES, x0 + 64 * s, y);
       bulk_commit();
+      if (C_::ROUNDS > 1) {  // a peer refills these slots in the next phase: tell the MMA thread when the store has read them
+        bulk_wait_read<0>();
+        mbar_arrive(c.bars + OFF_STORE_DONE);
+      }
     }
   }
+  return stop;
 }
 
 // ---- epilogue global-memory traffic ---------------------------------------------------------------------------

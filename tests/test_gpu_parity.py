@@ -35,7 +35,11 @@ def random_case(N, B, T, a_dim, act, seed, alpha=0.1, scale=None, pad_cols=False
     if pad_cols:
         A[:, :, 2:] = 0.0
     r0 = torch.rand(B, N, generator=g) - 0.5  # zero mean keeps J0*sum(r) small, so the activations are not saturated
-    return A, Wa, Wo, r0, -0.1, 0.1, alpha, act
+    # Global inhibition feeds the population mean back with loop gain alpha*|J0|*N*F': beyond N ~ 128 the reference's
+    # J0 = -0.1 makes that mode of a random network unstable, and rounding differences between two correct evaluations
+    # then double every step.  The random parity cases keep the gain below one; the reference's own J0 is exercised
+    # by the benchmark-like cases further down.
+    return A, Wa, Wo, r0, -0.1 * min(1.0, 128.0 / N), 0.1, alpha, act
 
 
 FWD_SHAPES = [
@@ -52,6 +56,14 @@ FWD_SHAPES = [
     (512, 260, 6, 2, "gelu", False),     # CTA pairs, cluster of 8, two 256-sample tiles (one mostly padding)
     (384, 700, 4, 2, "tanh", False),     # N padded to 512, three tiles
     (100, 513, 7, 2, "silu", False),     # five tiles, the last with one valid sample; weights resident in shared memory
+    (1024, 130, 6, 2, "gelu", False),    # two K rounds per step (16 chunks through 8 slots), cluster of 8, two tiles
+    (640, 300, 5, 2, "tanh", False),     # N padded to 1024, three tiles
+    (1024, 16, 3, 2, "silu", False),
+    # more tiles than clusters can be resident (148 / 33 / 15 for clusters of 1 / 4 / 8): every cluster runs several
+    # tiles back to back, the first step of each fed by TMA instead of by the previous step's epilogue
+    (64, 19200, 9, 2, "tanh", False),
+    (512, 4352, 3, 2, "tanh", False),
+    (1024, 2048, 3, 2, "silu", False),
     # (relu is covered by the shapes above and by the benchmark-like cases below; with zero-mean random states many
     # pre-activations sit within bf16 rounding of relu's kink, where F' jumps between 0 and 1, so gradients of a
     # long random case differ from fp32 by a few percent in ANY bf16 implementation -- not a parity defect)
@@ -79,6 +91,12 @@ def test_forward_and_backward_match_oracle(shape):
     cot = torch.randn(T, B, N, generator=g)
     ref = orc.ring_backward_manual(cot.double(), A.double(), Wa.double(), J0, J1, Wo.double(), ref_hist,
                                    r0.double(), alpha, act)
+    # The reference computes in fp32; the expected values here are its algorithm in double precision.  The distance
+    # between the two (rounding of the reference's own arithmetic, ~1e-6 at small N, ~1e-4 for the N*N*B*T-term sums
+    # at N = 1024) is added to the stated tolerance: two correct fp32 evaluations can differ by that much.
+    hist32 = orc.ring_forward_lean(A, Wa, J0, J1, Wo, r0, alpha, act)
+    ref32 = orc.ring_backward_manual(cot, A, Wa, J0, J1, Wo, hist32, r0, alpha, act)
+    noise = {k: orc.rel_err(ref32[k], ref[k]) for k in ("dWo", "dWa", "dr_init", "dA")}
     dA, dWa_, dWo_, dr0, dcot = _dev(A, Wa, Wo, r0, cot)
     for prec in _modes_for(N, B, T, a_dim, 2 if pad else a_dim):
         tol = TOL[prec]
@@ -89,11 +107,11 @@ def test_forward_and_backward_match_oracle(shape):
         assert orc.rel_err(f["final"], ref_hist[-1]) < tol
         b = run_backward(dA, dWa_, dWo_, dr0, J0, J1, alpha, act, f, grad_output=dcot, prec=prec, active=active)
         assert all(canaries_intact(x) for x in b["backs"]), "backward wrote outside its outputs"
-        assert orc.rel_err(b["dWo"], ref["dWo"]) < tol, prec
-        assert orc.rel_err(b["dWa"], ref["dWa"]) < tol, prec
+        assert orc.rel_err(b["dWo"], ref["dWo"]) < tol + noise["dWo"], prec
+        assert orc.rel_err(b["dWa"], ref["dWa"]) < tol + noise["dWa"], prec
         # the gradient w.r.t. the initial state (the reference returns none) has crossed every step's bf16 rounding of
         # delta without the averaging over (t, b) that the weight gradients enjoy: twice the bound in bf16 mode
-        assert orc.rel_err(b["dr_init"], ref["dr_init"]) < (tol if prec == "fp32" else 2 * tol), prec
+        assert orc.rel_err(b["dr_init"], ref["dr_init"]) < (tol if prec == "fp32" else 2 * tol) + noise["dr_init"], prec
         # dJ0 = sum_ij G_ij and dJ1 = <G, Wo> (G = dWo / J1) are sums with heavy cancellation: the bound is the
         # tolerance times the magnitude of the terms (Cauchy-Schwarz), not of the cancelled result
         G = ref["dWo"] / J1
@@ -101,10 +119,10 @@ def test_forward_and_backward_match_oracle(shape):
         assert abs(float(b["dJ"][1]) - float(ref["dJ1"])) < tol * max(1.0, float(G.norm()) * float(Wo.norm()))
         if pad:
             assert float(b["dWa"][2:].abs().max()) == 0.0  # skipped columns: exactly zero
-            assert orc.rel_err(b["dA"][:, :, :2], ref["dA"][:, :, :2]) < (tol if prec == "fp32" else 2 * tol), prec
+            assert orc.rel_err(b["dA"][:, :, :2], ref["dA"][:, :, :2]) < (tol if prec == "fp32" else 2 * tol) + noise["dA"], prec
         else:
             # gradient w.r.t. the action signal (the reference returns none); per-(b,t) scalars, no averaging
-            assert orc.rel_err(b["dA"], ref["dA"]) < (tol if prec == "fp32" else 2 * tol), prec
+            assert orc.rel_err(b["dA"], ref["dA"]) < (tol if prec == "fp32" else 2 * tol) + noise["dA"], prec
         # same call again: bit-identical (no atomics anywhere)
         f2 = run_forward(dA, dWa_, dWo_, dr0, J0, J1, alpha, act, prec, active, history=True, decode=False)
         b2 = run_backward(dA, dWa_, dWo_, dr0, J0, J1, alpha, act, f2, grad_output=dcot, prec=prec, active=active)
@@ -167,7 +185,7 @@ def test_autograd_surface_against_reference_training_gradients(name):
 # in dWo at T=32 and any two precisions decorrelate at T=512 -- so that shape is compared at T=8, where errors are
 # still those of the arithmetic; (256, 192, 32) and (512, 192, 32, tanh) cover the longer horizon.
 FUSED_CASES = [(120, 128, 120, "tanh"), (24, 5, 12, "gelu"), (256, 64, 40, "relu"), (512, 192, 8, "gelu"),
-               (256, 192, 32, "gelu"), (512, 192, 32, "tanh")]
+               (256, 192, 32, "gelu"), (512, 192, 32, "tanh"), (1024, 192, 12, "tanh")]
 
 
 @pytest.mark.parametrize("cfg", FUSED_CASES, ids=lambda c: "N%d-B%d-T%d-%s" % c)
