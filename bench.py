@@ -34,7 +34,8 @@ WORKLOADS = {
     "c1": dict(N=120, B=128, T=120, act="tanh", max_av=0.1 * math.pi, cpu_slice=(128, 120)),
     "c2": dict(N=256, B=1024, T=256, act="relu", max_av=0.1 * math.pi, cpu_slice=(64, 32)),
     "c3": dict(N=512, B=4096, T=512, act="gelu", max_av=0.1 * math.pi, cpu_slice=(64, 16)),
-    "c4": dict(N=1024, B=8192, T=2000, act="tanh", max_av=0.05 * math.pi, cpu_slice=(16, 8)),
+    # defined on 8 GPUs (global batch 8192): B is the per-GPU shard, so --gpus 8 runs exactly the named configuration
+    "c4": dict(N=1024, B=1024, T=2000, act="tanh", max_av=0.05 * math.pi, cpu_slice=(16, 8), defined_on=8),
     # forward-only rollout with the ideal cosine weights; decoded-angle error against the integrated target
     "c5": dict(N=120, B=65536, T=4000, act="tanh", max_av=0.1 * math.pi, cpu_slice=(1024, 200), rollout=True),
 }
@@ -388,7 +389,10 @@ def run_ours(args, wl):
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": "bf16" if prec == "bf16" else "f32", "data": "synthetic",
         "config": {"workload": f"{args.workload}: N={N}, B={B_local} per GPU, T={T}, {act}, alpha=0.1, "
-                               f"fused fwd+loss+bwd, precision mode {prec}",
+                               f"fused fwd+loss+bwd, precision mode {prec}"
+                               + (f" (the configuration is defined on {wl['defined_on']} GPUs, global batch "
+                                  f"{wl['B'] * wl['defined_on']}; this run has {world})"
+                                  if wl.get("defined_on", world) != world and args.scaling == "weak" else ""),
                    "global_batch": B_global, "parallelism": f"dp{world}",
                    "l2": "working set (saved states + delta, several GB) exceeds the 126 MB L2; no flush needed"},
         "e2e": {"value": B_global * T / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
