@@ -2,7 +2,9 @@
 // (tc_fwd.cu, tc_bwd.cu, tc_gemm.cu), operand preparation and buffer layouts.
 //
 // Layouts (NP = N rounded up to 128/256/512/1024, BP = B rounded up to the tile height 128 (256 for CTA pairs), C = NP/128):
-//   weights, forward  Wf [C*2*RB, NP] bf16 (RB = 208, or 224 when CTA pairs are used, i.e. B > 128): block (q,s) rows = {Wo[i,:], Wl[i,:], Wr[i,:] for the 64 neurons i of
+//   weights, forward  Wf [C*2*NG*RB, NP] bf16 (NG = 1 weight group for up to two active action columns; with more, the
+//                     1 + n_act matrices come in NG = ceil((1+n_act)/3) groups of three and block (q,s,grp) follows
+//                     block (q,s,grp-1); described here for NG = 1) (RB = 208, or 224 when CTA pairs are used, i.e. B > 128): block (q,s) rows = {Wo[i,:], Wl[i,:], Wr[i,:] for the 64 neurons i of
 //                     sub-slice s of CTA q, a row of ones, zero rows}; columns j >= N zero
 //   weights, backward Wb, same shape: rows = {Wo[:,j], Wl[:,j], Wr[:,j] for the 64 neurons j, ones, zeros}
 //   saved             Rh [T+1][BP][NP] bf16 row-major (Rh[0] = r_init, Rh[t+1] = r_t; the last slot stays unwritten:
@@ -28,26 +30,35 @@ bool use_pairs(int B, int N) {
   static const bool on = getenv("RINGRNN_PAIRS") != nullptr && getenv("RINGRNN_PAIRS")[0] == '1';
   return on && B > 128 && N <= 512;
 }
-int padded_b(int B, int N) { return use_pairs(B, N) ? (B + 255) / 256 * 256 : (B + 127) / 128 * 128; }
+int padded_b(int B, int N, int n_act) {
+  return (use_pairs(B, N) && n_act <= 2) ? (B + 255) / 256 * 256 : (B + 127) / 128 * 128;
+}
 int n_active_of(const RingRnnProblem& p) { return p.n_active < 0 ? p.a_dim : p.n_active; }
 
-// Wf / Wb blocks, see the header comment.  grid (NP/64 column chunks, C*2 blocks), block 256
-__global__ void prep_weights_kernel(const float* __restrict__ Wo, const float* __restrict__ Wl,
-                                    const float* __restrict__ Wr, int N, int NP, int RB,
-                                    __nv_bfloat16* __restrict__ Wf, __nv_bfloat16* __restrict__ Wb) {
-  const int blk = blockIdx.y;  // q*2 + s
-  const int n_first = blk * 64;
+struct ActiveCols {
+  int n;
+  int c[RINGRNN_MAX_ACTIVE];
+};
+
+// Wf / Wb blocks, see the header comment.  grid (NP/64 column chunks, C*2*NG blocks), block 256.  Matrix 3*grp + m of
+// the list {Wo, Wa[cols[0]], Wa[cols[1]], ...} fills rows [64m, 64m+64) of block (q, s, grp); missing ones are zero.
+__global__ void prep_weights_kernel(const float* __restrict__ Wo, const float* __restrict__ Wa, ActiveCols cols, int ng,
+                                    int N, int NP, int RB, __nv_bfloat16* __restrict__ Wf,
+                                    __nv_bfloat16* __restrict__ Wb) {
+  const int blk = blockIdx.y;  // (q*2 + s)*ng + grp
+  const int grp = blk % ng;
+  const int n_first = (blk / ng) * 64;
   for (int idx = threadIdx.x; idx < RB * 64; idx += blockDim.x) {
     const int rr = idx / 64, k = blockIdx.x * 64 + idx % 64;
     float vf = 0.f, vb = 0.f;
     if (rr < 192) {
-      const int m = rr / 64, n = n_first + rr % 64;
-      const float* W = (m == 0) ? Wo : (m == 1) ? Wl : Wr;
+      const int mi = 3 * grp + rr / 64, n = n_first + rr % 64;
+      const float* W = (mi == 0) ? Wo : (mi - 1 < cols.n ? Wa + (size_t)cols.c[mi - 1] * N * N : nullptr);
       if (W != nullptr && n < N && k < N) {
         vf = W[(size_t)n * N + k];
         vb = W[(size_t)k * N + n];
       }
-    } else if (rr == SUM_COL) {
+    } else if (rr == SUM_COL && grp == 0) {
       vf = vb = (k < N) ? 1.f : 0.f;
     }
     const size_t at = ((size_t)blk * RB + rr) * NP + k;
@@ -85,6 +96,7 @@ __global__ void dec_reduce_kernel(const float* __restrict__ part, int slots, int
 
 struct Layout {
   int NP, BP, C, RB, tile_rows;
+  int n_act, ng;   // active action columns; weight groups of three matrices (1 for up to two columns)
   bool pair;
   size_t w_bytes, r0_bytes, dec_bytes, state_bytes;
 };
@@ -92,12 +104,14 @@ struct Layout {
 Layout layout_of(const RingRnnProblem& p) {
   Layout l;
   l.NP = padded_n(p.N);
-  l.BP = padded_b(p.B, p.N);
+  l.BP = padded_b(p.B, p.N, n_active_of(p));
   l.C = l.NP / 128;
-  l.pair = use_pairs(p.B, p.N);
+  l.n_act = n_active_of(p);
+  l.ng = l.n_act <= 2 ? 1 : (1 + l.n_act + 2) / 3;
+  l.pair = use_pairs(p.B, p.N) && l.ng == 1;
   l.RB = block_rows(l.pair);
   l.tile_rows = l.pair ? 256 : 128;
-  l.w_bytes = align_up((size_t)l.C * 2 * l.RB * l.NP * 2, 1024);
+  l.w_bytes = align_up((size_t)l.C * 2 * l.ng * l.RB * l.NP * 2, 1024);
   l.r0_bytes = align_up((size_t)l.BP * l.NP * 2, 1024);
   l.dec_bytes = align_up((size_t)2 * l.C * 3 * p.T * l.BP * 4, 1024);
   l.state_bytes = align_up((size_t)l.BP * l.NP * 2, 1024);  // one time slot of Rh / Dh
@@ -106,8 +120,10 @@ Layout layout_of(const RingRnnProblem& p) {
 
 }  // namespace
 
+// N <= 1024 with up to two active action columns; N <= 512 with up to RINGRNN_MAX_ACTIVE of them
 bool bf16_supported(const RingRnnProblem& p) {
-  return padded_n(p.N) != 0 && n_active_of(p) <= 2 && p.B >= 1 && p.T >= 1;
+  const int NP = padded_n(p.N), n_act = n_active_of(p);
+  return NP != 0 && p.B >= 1 && p.T >= 1 && (n_act <= 2 || (NP <= 512 && n_act <= RINGRNN_MAX_ACTIVE));
 }
 
 // FWD workspace: status(1024) | Wf | R0 | dec partials
@@ -145,11 +161,12 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   if (train) R0 = Rh;  // slot 0 of the saved state doubles as the initial A operand
 
   if (a.status == nullptr) RINGRNN_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), s));
-  const float* Wl = dp.n_mat > 1 ? dp.Wa + (size_t)dp.cols[0] * p.N * p.N : nullptr;
-  const float* Wr = dp.n_mat > 2 ? dp.Wa + (size_t)dp.cols[1] * p.N * p.N : nullptr;
+  ActiveCols ac;
+  ac.n = dp.n_mat - 1;
+  for (int k = 0; k < ac.n; ++k) ac.c[k] = dp.cols[k];
   {
     LaunchScope ls(K_PREP, s);
-    prep_weights_kernel<<<dim3(l.NP / 64, l.C * 2), 256, 0, s>>>(p.Wo, Wl, Wr, p.N, l.NP, l.RB, Wf, nullptr);
+    prep_weights_kernel<<<dim3(l.NP / 64, l.C * 2 * l.ng), 256, 0, s>>>(p.Wo, dp.Wa, ac, l.ng, p.N, l.NP, l.RB, Wf, nullptr);
   }
   RINGRNN_CUDA_TRY(cudaGetLastError());
   {
@@ -159,7 +176,7 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   RINGRNN_CUDA_TRY(cudaGetLastError());
 
   CUtensorMap tmW, tmR0;
-  if (!make_tmap_bf16_2d(&tmW, Wf, (uint64_t)l.C * 2 * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, 64))
+  if (!make_tmap_bf16_2d(&tmW, Wf, (uint64_t)l.C * 2 * l.ng * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, 64))
     return RINGRNN_ERR_CUDA;
   // one map serves the initial-state loads (rows [0, BP)) and, in training, the saved-state stores (rows up to T*BP)
   if (!make_tmap_bf16_2d(&tmR0, R0, (uint64_t)(train ? p.T + 1 : 1) * l.BP, (uint64_t)l.NP, 128, 64))
@@ -171,6 +188,8 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   fp.B = p.B; fp.T = p.T; fp.N = p.N; fp.BP = l.BP; fp.a_dim = p.a_dim;
   fp.colL = dp.n_mat > 1 ? dp.cols[0] : -1;
   fp.colR = dp.n_mat > 2 ? dp.cols[1] : -1;
+  fp.ng = l.ng; fp.n_act = ac.n;
+  for (int k = 0; k < ac.n; ++k) fp.cols[k] = ac.c[k];
   fp.n_tiles = l.BP / l.tile_rows;
   fp.J0 = p.J0; fp.J1 = p.J1; fp.alpha = p.alpha;
   fp.A = p.A; fp.r_init = p.r_init;
@@ -194,9 +213,9 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
 
 namespace {
 
-// dWcat [3*NP][NP] -> grad_Wo = J1 * block 0, grad_Wa[colL] = block 1, grad_Wa[colR] = block 2 (unpadded);
+// dWcat [(1+n)*NP][NP] -> grad_Wo = J1 * block 0, grad_Wa[cols[k]] = block 1 + k (unpadded);
 // raw = block 0 unscaled and unpadded (for the J0 / J1 gradients)
-__global__ void unpack_dw_kernel(const float* __restrict__ dWcat, int N, int NP, float J1, int colL, int colR,
+__global__ void unpack_dw_kernel(const float* __restrict__ dWcat, int N, int NP, float J1, ActiveCols cols,
                                  float* grad_Wo, float* grad_Wa, float* raw) {
   const size_t NN = (size_t)N * N;
   for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < NN; e += (size_t)gridDim.x * blockDim.x) {
@@ -204,13 +223,13 @@ __global__ void unpack_dw_kernel(const float* __restrict__ dWcat, int N, int NP,
     const float g0 = dWcat[(size_t)i * NP + j];
     grad_Wo[e] = J1 * g0;
     raw[e] = g0;
-    if (colL >= 0) grad_Wa[(size_t)colL * NN + e] = dWcat[((size_t)NP + i) * NP + j];
-    if (colR >= 0) grad_Wa[(size_t)colR * NN + e] = dWcat[((size_t)2 * NP + i) * NP + j];
+    for (int k = 0; k < cols.n; ++k) grad_Wa[(size_t)cols.c[k] * NN + e] = dWcat[((size_t)(1 + k) * NP + i) * NP + j];
   }
 }
 
 int gemm_splits(const Layout& l, int T) {
-  const int tiles = (3 * l.NP / 128) * (l.NP > 512 ? l.NP / 512 : 1);
+  const int blocks = l.ng == 1 ? 3 : 1 + l.n_act;  // column blocks of DL = row blocks of dWcat
+  const int tiles = (blocks * l.NP / 128) * (l.NP > 512 ? l.NP / 512 : 1);
   int ns = 148 / tiles;
   const long long K = (long long)T * l.BP;
   while (ns > 1 && K / ns < 256) --ns;
@@ -219,22 +238,22 @@ int gemm_splits(const Layout& l, int T) {
 
 struct BwdLayout {
   size_t w_bytes, dl_bytes, partial_bytes, dw_bytes, raw_bytes, da_bytes;
-  int nsplit;
+  int nsplit, blocks, da_slots, da_per_slot;
 };
 
-// grad_A[b,t,col] = sum over slots of part[slot][k][t][b], k = 0 -> colL, k = 1 -> colR
-__global__ void da_reduce_kernel(const float* __restrict__ part, int slots, int B, int T, int BP, int a_dim, int colL,
-                                 int colR, float* grad_A) {
+// grad_A[b,t,cols[k]] = sum over slots of part[slot][k][t][b]   (`per_slot` entries k per slot, of which the first
+// cols.n are used)
+__global__ void da_reduce_kernel(const float* __restrict__ part, int slots, int per_slot, int B, int T, int BP, int a_dim,
+                                 ActiveCols cols, float* grad_A) {
   const size_t total = (size_t)B * T;
   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const int t = (int)(idx / B), b = (int)(idx % B);
-    float acc[2] = {0.f, 0.f};
-    for (int sl = 0; sl < slots; ++sl)
-#pragma unroll
-      for (int k = 0; k < 2; ++k) acc[k] += part[(((size_t)sl * 2 + k) * T + t) * BP + b];
     float* o = grad_A + ((size_t)b * T + t) * a_dim;
-    if (colL >= 0) o[colL] = acc[0];
-    if (colR >= 0) o[colR] = acc[1];
+    for (int k = 0; k < cols.n; ++k) {
+      float acc = 0.f;
+      for (int sl = 0; sl < slots; ++sl) acc += part[(((size_t)sl * per_slot + k) * T + t) * BP + b];
+      o[cols.c[k]] = acc;
+    }
   }
 }
 
@@ -242,11 +261,15 @@ BwdLayout bwd_layout_of(const RingRnnProblem& p, const Layout& l) {
   BwdLayout b;
   b.nsplit = gemm_splits(l, p.T);
   b.w_bytes = l.w_bytes;
-  b.dl_bytes = align_up((size_t)p.T * l.BP * 3 * l.NP * 2, 1024);
-  b.partial_bytes = align_up((size_t)b.nsplit * 3 * l.NP * l.NP * 4, 1024);
-  b.dw_bytes = align_up((size_t)3 * l.NP * l.NP * 4, 1024);
+  b.blocks = l.ng == 1 ? 3 : 1 + l.n_act;
+  b.dl_bytes = align_up((size_t)p.T * l.BP * b.blocks * l.NP * 2, 1024);
+  b.partial_bytes = align_up((size_t)b.nsplit * b.blocks * l.NP * l.NP * 4, 1024);
+  b.dw_bytes = align_up((size_t)b.blocks * l.NP * l.NP * 4, 1024);
   b.raw_bytes = align_up((size_t)p.N * p.N * 4, 1024);
-  b.da_bytes = align_up((size_t)2 * l.C * 2 * p.T * l.BP * 4, 1024);
+  // dL/dA partial sums: [2C][2] (up to two columns) or [4C][n_act] entries of T*BP floats
+  b.da_slots = l.ng == 1 ? 2 * l.C : 4 * l.C;
+  b.da_per_slot = l.ng == 1 ? 2 : l.n_act;
+  b.da_bytes = align_up((size_t)b.da_slots * b.da_per_slot * p.T * l.BP * 4, 1024);
   return b;
 }
 
@@ -286,22 +309,25 @@ int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   const __nv_bfloat16* Dh = Rh + (size_t)(p.T + 1) * l.BP * l.NP;
 
   if (a.status == nullptr) RINGRNN_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), s));
-  const float* Wl = dp.n_mat > 1 ? dp.Wa + (size_t)dp.cols[0] * p.N * p.N : nullptr;
-  const float* Wr = dp.n_mat > 2 ? dp.Wa + (size_t)dp.cols[1] * p.N * p.N : nullptr;
   const int colL = dp.n_mat > 1 ? dp.cols[0] : -1, colR = dp.n_mat > 2 ? dp.cols[1] : -1;
+  ActiveCols ac;
+  ac.n = dp.n_mat - 1;
+  for (int k = 0; k < ac.n; ++k) ac.c[k] = dp.cols[k];
   {
     LaunchScope ls(K_PREP, s);
-    prep_weights_kernel<<<dim3(l.NP / 64, l.C * 2), 256, 0, s>>>(p.Wo, Wl, Wr, p.N, l.NP, l.RB, nullptr, Wb);
+    prep_weights_kernel<<<dim3(l.NP / 64, l.C * 2 * l.ng), 256, 0, s>>>(p.Wo, dp.Wa, ac, l.ng, p.N, l.NP, l.RB, nullptr, Wb);
   }
   RINGRNN_CUDA_TRY(cudaGetLastError());
   CUtensorMap tmW;
-  if (!make_tmap_bf16_2d(&tmW, Wb, (uint64_t)l.C * 2 * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, 64))
+  if (!make_tmap_bf16_2d(&tmW, Wb, (uint64_t)l.C * 2 * l.ng * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, 64))
     return RINGRNN_ERR_CUDA;
 
   TcBwdParams bp;
   memset(&bp, 0, sizeof(bp));
   bp.B = p.B; bp.T = p.T; bp.N = p.N; bp.BP = l.BP; bp.a_dim = p.a_dim;
   bp.colL = colL; bp.colR = colR;
+  bp.ng = l.ng; bp.n_act = ac.n;
+  for (int k = 0; k < ac.n; ++k) bp.cols[k] = ac.c[k];
   bp.n_tiles = l.BP / l.tile_rows;
   bp.J0 = p.J0; bp.J1 = p.J1; bp.alpha = p.alpha;
   bp.A = p.A; bp.Dh = Dh;
@@ -315,24 +341,24 @@ int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   bp.dA_part = a.grad_A != nullptr ? dA_part : nullptr;
   bp.status = status;
   CUtensorMap tmDL;
-  if (!make_tmap_bf16_2d(&tmDL, DL, (uint64_t)p.T * l.BP, (uint64_t)3 * l.NP, 128, 64)) return RINGRNN_ERR_CUDA;
+  if (!make_tmap_bf16_2d(&tmDL, DL, (uint64_t)p.T * l.BP, (uint64_t)bl.blocks * l.NP, 128, 64)) return RINGRNN_ERR_CUDA;
   int rc = tc_backward_launch(l.NP, l.pair, tmW, tmDL, bp, s);
   if (rc != RINGRNN_OK) return rc;
 
   if (a.grad_A != nullptr) {
     RINGRNN_CUDA_TRY(cudaMemsetAsync(a.grad_A, 0, sizeof(float) * (size_t)p.B * p.T * p.a_dim, s));
     LaunchScope ls(K_REDUCE, s);
-    da_reduce_kernel<<<296, 256, 0, s>>>(dA_part, 2 * l.C, p.B, p.T, l.BP, p.a_dim, colL, colR, a.grad_A);
+    da_reduce_kernel<<<296, 256, 0, s>>>(dA_part, bl.da_slots, bl.da_per_slot, p.B, p.T, l.BP, p.a_dim, ac, a.grad_A);
     RINGRNN_CUDA_TRY(cudaGetLastError());
   }
-  // dWcat[3NP, NP] = DL^T [3NP, T*BP] x Rh[0..T) [T*BP, NP]
-  rc = tc_gemm(1, DL, Rh, partial, dWcat, 3 * l.NP, l.NP, (long long)p.T * l.BP, bl.nsplit, status, s);
+  // dWcat[blocks*NP, NP] = DL^T [blocks*NP, T*BP] x Rh[0..T) [T*BP, NP]
+  rc = tc_gemm(1, DL, Rh, partial, dWcat, bl.blocks * l.NP, l.NP, (long long)p.T * l.BP, bl.nsplit, status, s);
   if (rc != RINGRNN_OK) return rc;
   const size_t NN = (size_t)p.N * p.N;
   RINGRNN_CUDA_TRY(cudaMemsetAsync(a.grad_Wa, 0, sizeof(float) * (size_t)p.a_dim * NN, s));
   {
     LaunchScope ls(K_REDUCE, s);
-    unpack_dw_kernel<<<296, 256, 0, s>>>(dWcat, p.N, l.NP, p.J1, colL, colR, a.grad_Wo, a.grad_Wa, raw);
+    unpack_dw_kernel<<<296, 256, 0, s>>>(dWcat, p.N, l.NP, p.J1, ac, a.grad_Wo, a.grad_Wa, raw);
   }
   RINGRNN_CUDA_TRY(cudaGetLastError());
   if (a.grad_J != nullptr) {

@@ -20,12 +20,17 @@ using namespace tc;
 using namespace tcr;
 
 
-template <int NP, bool PAIR>
+// GEN: more than two active action columns -- the transposed weights come in p.ng groups of three matrices, the
+// carry is gathered over the groups, and DL gets one scaled copy of delta per active column.
+template <int NP, bool PAIR, bool GEN>
 __global__ void __launch_bounds__(THREADS, 1)
 bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmDL, const TcBwdParams p) {
   using C_ = Cfg<NP, PAIR>;
+  static_assert(!GEN || (C_::ROUNDS == 1 && !PAIR), "weight groups: one K round, single CTAs");
   extern __shared__ uint8_t smem_raw[];
   const Ctx<NP, PAIR> c = setup_cta<NP, PAIR>(smem_raw, p.dec_u, p.dec_v, p.N, p.status);
+  const int ng = GEN ? p.ng : 1;
+  const int dl_blocks = GEN ? 1 + p.n_act : 3;  // column blocks of NP in a row of DL
   const uint32_t bars = c.bars, tmem_base = c.tmem_base;
   const WaitCtx& wctx = c.wctx;
   float* uv = c.uv;
@@ -39,9 +44,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   if (warp < 4) {
     reg_dec<40>();
     if (warp == 0 && lane == 0) {
-      producer_loop<NP, PAIR>(c, &tmW, total_steps, 302);
+      producer_loop<NP, PAIR>(c, &tmW, total_steps, 302, ng);
     } else if (warp == 1 && lane == 0) {
-      if (c.leader) mma_loop<NP, PAIR, false>(c, total_steps, T, 310, true);
+      if (c.leader) mma_loop<NP, PAIR, false>(c, total_steps, T, 310, true, ng);
     } else if (warp == 2 && lane == 0) {
       relay_loop<NP, PAIR, false>(c, total_steps, T, 320, [](int, int) {});
     }
@@ -76,8 +81,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         Ln = 0.f; Rn = 0.f; cx = 0.f; cy = 0.f; cs = 0.f;
         if (valid) {
           const float* at = p.A + ((size_t)b * T + t) * p.a_dim;
-          if (p.colL >= 0) Ln = __ldg(at + p.colL);
-          if (p.colR >= 0) Rn = __ldg(at + p.colR);
+          if (!GEN && p.colL >= 0) Ln = __ldg(at + p.colL);
+          if (!GEN && p.colR >= 0) Rn = __ldg(at + p.colR);
           if (has_coef) {
             cx = __ldg(p.coef_x + (size_t)b * T + t);
             cy = __ldg(p.coef_y + (size_t)b * T + t);
@@ -157,23 +162,44 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         // off the critical path: [delta | L*delta | R*delta] for the weight-gradient GEMM.  The scaled copies are
         // formed from the bf16 delta the MMA sees, so the three blocks are consistent with one another.
         const uint32_t stage = c.stage_base + (uint32_t)(warp - 4) * 2048u;
+        const size_t dl_row_bytes = (size_t)dl_blocks * NP * 2;
+        if constexpr (!GEN) {
 #pragma unroll
-        for (int s = 0; s < 2; ++s) {
-          // row 0 of this warp's 32-row block, first of this thread's 32 columns, column block 0
-          uint8_t* blk0 = reinterpret_cast<uint8_t*>(p.DL + ((size_t)t * p.BP + (b - lane)) * (3 * NP) + nq + 64 * s);
-          uint32_t o[16];
+          for (int s = 0; s < 2; ++s) {
+            // row 0 of this warp's 32-row block, first of this thread's 32 columns, column block 0
+            uint8_t* blk0 = reinterpret_cast<uint8_t*>(p.DL + ((size_t)t * p.BP + (b - lane)) * (3 * NP) + nq + 64 * s);
+            uint32_t o[16];
 #pragma unroll
-          for (int w = 0; w < 16; ++w) {
-            const uint32_t d2 = packed[s * 16 + w];
-            o[w] = pack_bf16x2(L * bf16_lo(d2), L * bf16_hi(d2));
+            for (int w = 0; w < 16; ++w) {
+              const uint32_t d2 = packed[s * 16 + w];
+              o[w] = pack_bf16x2(L * bf16_lo(d2), L * bf16_hi(d2));
+            }
+            store_rows_via_smem(stage, lane, o, blk0 + (size_t)NP * 2, dl_row_bytes);
+#pragma unroll
+            for (int w = 0; w < 16; ++w) {
+              const uint32_t d2 = packed[s * 16 + w];
+              o[w] = pack_bf16x2(R * bf16_lo(d2), R * bf16_hi(d2));
+            }
+            store_rows_via_smem(stage, lane, o, blk0 + (size_t)2 * NP * 2, dl_row_bytes);
           }
-          store_rows_via_smem(stage, lane, o, blk0 + (size_t)NP * 2, (size_t)3 * NP * 2);
+        } else {
+          // one scaled copy per active column: block 1 + k = A[b,t,cols[k]] * delta_t
+          const float* at = p.A + ((size_t)b * T + t) * p.a_dim;
+          for (int k = 0; k < p.n_act; ++k) {
+            const float ak = valid ? __ldg(at + p.cols[k]) : 0.f;
 #pragma unroll
-          for (int w = 0; w < 16; ++w) {
-            const uint32_t d2 = packed[s * 16 + w];
-            o[w] = pack_bf16x2(R * bf16_lo(d2), R * bf16_hi(d2));
+            for (int s = 0; s < 2; ++s) {
+              uint8_t* blk0 = reinterpret_cast<uint8_t*>(p.DL + ((size_t)t * p.BP + (b - lane)) * ((size_t)dl_blocks * NP) +
+                                                         nq + 64 * s);
+              uint32_t o[16];
+#pragma unroll
+              for (int w = 0; w < 16; ++w) {
+                const uint32_t d2 = packed[s * 16 + w];
+                o[w] = pack_bf16x2(ak * bf16_lo(d2), ak * bf16_hi(d2));
+              }
+              store_rows_via_smem(stage, lane, o, blk0 + (size_t)(1 + k) * NP * 2, dl_row_bytes);
+            }
           }
-          store_rows_via_smem(stage, lane, o, blk0 + (size_t)2 * NP * 2, (size_t)3 * NP * 2);
         }
       };
 
@@ -186,6 +212,70 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         float c0 = 0.f, dAl = 0.f, dAr = 0.f;
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
+          if constexpr (GEN) {
+            // carry of sub-slice s gathered over the weight groups; one accumulator per (s, group)
+            const float* at = p.A + ((size_t)b * T + t) * p.a_dim;
+            for (int grp = 0; grp < ng; ++grp) {
+              const int i0 = 3 * grp - 1;  // index into cols[] of the group's first matrix (-1: Wo)
+              float k0, k1 = 0.f, k2 = 0.f;
+              k0 = (grp == 0) ? J1 : ((valid && i0 < p.n_act) ? __ldg(at + p.cols[i0]) : 0.f);
+              if (valid && i0 + 1 < p.n_act) k1 = __ldg(at + p.cols[i0 + 1]);
+              if (valid && i0 + 2 < p.n_act) k2 = __ldg(at + p.cols[i0 + 2]);
+              const uint32_t pass = (g * 2u + (uint32_t)s) * (uint32_t)ng + (uint32_t)grp, acc = pass & 1u;
+              mbar_wait(bars + OFF_D_FULL + 8 * acc, (pass >> 1) & 1u, wctx, 307);
+              tcgen05_fence_after();
+              if (s == 0 && grp == 0) {
+                uint32_t sraw;
+                tmem_ld1(tmem_base + lane_base + acc * 256 + SUM_COL, &sraw);  // sum_i delta_t[b,i]
+                tmem_ld_wait();
+                c0 = J0 * __uint_as_float(sraw);
+              }
+              float da0 = 0.f, da1 = 0.f, da2 = 0.f;
+#pragma unroll
+              for (int c16 = 0; c16 < 2; ++c16) {
+                uint32_t z0[16], z1[16], z2[16];
+                const uint32_t col = tmem_base + lane_base + acc * 256 + 32 * h + 16 * c16;
+                tmem_ld16(col, z0);
+                tmem_ld16(col + 64, z1);
+                tmem_ld16(col + 128, z2);
+                tmem_ld_wait();
+                if (want_dA) {
+                  // dL/dA[b,t,col] = sum_j r_{t-1}[j] (delta_t W_col)[j]: this thread's 16 columns
+                  const uint4* rsrc = reinterpret_cast<const uint4*>(p.Rh + ((size_t)t * p.BP + b) * NP + nq + 64 * s + 16 * c16);
+                  const uint4 r0 = __ldg(rsrc), r1 = __ldg(rsrc + 1);
+                  const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) {
+                    const float rp = (j & 1) ? bf16_hi(rw[j >> 1]) : bf16_lo(rw[j >> 1]);
+                    da0 = fmaf(rp, __uint_as_float(z0[j]), da0);
+                    da1 = fmaf(rp, __uint_as_float(z1[j]), da1);
+                    da2 = fmaf(rp, __uint_as_float(z2[j]), da2);
+                  }
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const int idx = s * 32 + c16 * 16 + j;
+                  float cv = (grp == 0) ? fmaf(beta, master[idx], c0) : master[idx];
+                  cv = fmaf(k0, __uint_as_float(z0[j]), cv);
+                  cv = fmaf(k1, __uint_as_float(z1[j]), cv);
+                  cv = fmaf(k2, __uint_as_float(z2[j]), cv);
+                  master[idx] = (nq + 64 * s + c16 * 16 + j < p.N) ? cv : 0.f;
+                }
+              }
+              release_accumulator<NP, PAIR>(c, (int)acc, lane);
+              if (want_dA) {
+                // partial sums [slot = ((2q+h)*2+s)][k][t][b] of the group's action matrices
+                const size_t slot4 = (size_t)((2 * q + h) * 2 + s);
+                const float dav[3] = {da0, da1, da2};
+#pragma unroll
+                for (int m = 0; m < 3; ++m) {
+                  const int k = i0 + m;
+                  if (k >= 0 && k < p.n_act) p.dA_part[((slot4 * p.n_act + k) * T + t) * p.BP + b] = dav[m];
+                }
+              }
+            }
+            continue;
+          }
           mbar_wait(bars + OFF_D_FULL + 8 * s, g & 1u, wctx, 307);
           if (warp == 4 && lane == 0) RINGRNN_STAMP(g, s == 0 ? 5 : 7);
           tcgen05_fence_after();
@@ -229,7 +319,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           release_accumulator<NP, PAIR>(c, s, lane);
           if (warp == 4 && lane == 0) RINGRNN_STAMP(g, s == 0 ? 6 : 8);
         }
-        if (want_dA) {
+        if (!GEN && want_dA) {
           float* dp = p.dA_part + (((size_t)(2 * q + h) * 2) * T + t) * p.BP + b;
           dp[0] = dAl;
           dp[(size_t)T * p.BP] = dAr;
@@ -256,10 +346,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   teardown_cta<NP, PAIR>(c);
 }
 
-template <int NP, bool PAIR>
+template <int NP, bool PAIR, bool GEN = false>
 static int launch_bwd_tc(const CUtensorMap& tmW, const CUtensorMap& tmDL, const TcBwdParams& p, cudaStream_t s) {
   using C_ = Cfg<NP, PAIR>;
-  auto kernel = bwd_tc_kernel<NP, PAIR>;
+  auto kernel = bwd_tc_kernel<NP, PAIR, GEN>;
   RINGRNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM));
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -284,6 +374,13 @@ static int launch_bwd_tc(const CUtensorMap& tmW, const CUtensorMap& tmDL, const 
 
 int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmDL, const TcBwdParams& p,
                        cudaStream_t s) {
+  if (p.ng > 1) {  // more than two active action columns
+    if (pair) return RINGRNN_ERR_UNSUPPORTED;
+    if (NP == 128) return launch_bwd_tc<128, false, true>(tmW, tmDL, p, s);
+    if (NP == 256) return launch_bwd_tc<256, false, true>(tmW, tmDL, p, s);
+    if (NP == 512) return launch_bwd_tc<512, false, true>(tmW, tmDL, p, s);
+    return RINGRNN_ERR_UNSUPPORTED;
+  }
   if (NP == 128) return pair ? launch_bwd_tc<128, true>(tmW, tmDL, p, s) : launch_bwd_tc<128, false>(tmW, tmDL, p, s);
   if (NP == 256) return pair ? launch_bwd_tc<256, true>(tmW, tmDL, p, s) : launch_bwd_tc<256, false>(tmW, tmDL, p, s);
   if (NP == 512) return pair ? launch_bwd_tc<512, true>(tmW, tmDL, p, s) : launch_bwd_tc<512, false>(tmW, tmDL, p, s);

@@ -18,12 +18,16 @@ using namespace tc;
 using namespace tcr;
 
 
-template <int ACT, int NP, bool PAIR>
+// GEN: more than two active action columns -- the weights come in p.ng groups of three matrices, and the epilogue
+// gathers the pre-activation over the groups before it applies F (one K round, no CTA pairs).
+template <int ACT, int NP, bool PAIR, bool GEN>
 __global__ void __launch_bounds__(THREADS, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmR0, const TcFwdParams p) {
   using C_ = Cfg<NP, PAIR>;
+  static_assert(!GEN || (C_::ROUNDS == 1 && !PAIR), "weight groups: one K round, single CTAs");
   extern __shared__ uint8_t smem_raw[];
   const Ctx<NP, PAIR> c = setup_cta<NP, PAIR>(smem_raw, p.dec_u, p.dec_v, p.N, p.status);
+  const int ng = GEN ? p.ng : 1;
   const uint32_t a_base = c.a_base, bars = c.bars, tmem_base = c.tmem_base;
   const WaitCtx& wctx = c.wctx;
   float* uv = c.uv;
@@ -37,9 +41,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   if (warp < 4) {
     reg_dec<40>();
     if (warp == 0 && lane == 0) {
-      producer_loop<NP, PAIR>(c, &tmW, total_steps, 202);
+      producer_loop<NP, PAIR>(c, &tmW, total_steps, 202, ng);
     } else if (warp == 1 && lane == 0) {
-      if (c.leader) mma_loop<NP, PAIR, true>(c, total_steps, T, 210, p.Rh != nullptr);
+      if (c.leader) mma_loop<NP, PAIR, true>(c, total_steps, T, 210, p.Rh != nullptr, ng);
     } else if (warp == 2 && lane == 0) {
       tma_prefetch_desc(&tmR0);
       relay_loop<NP, PAIR, true>(c, total_steps, T, 220, [&](int it, int round) {
@@ -82,9 +86,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           master[s * 32 + j] = (valid && n < p.N) ? __ldg(p.r_init + (size_t)b * p.N + n) : 0.f;
         }
       for (int t = 0; t < T; ++t, ++g) {
+        const float* at = p.A + ((size_t)b * T + t) * p.a_dim;  // this sample's action scalars (read only if valid)
         float L = 0.f, R = 0.f;
-        if (valid) {
-          const float* at = p.A + ((size_t)b * T + t) * p.a_dim;
+        if (!GEN && valid) {
           if (p.colL >= 0) L = __ldg(at + p.colL);
           if (p.colR >= 0) R = __ldg(at + p.colR);
         }
@@ -92,32 +96,77 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         float px = 0.f, py = 0.f, pa = 0.f, c0 = 0.f;
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
-          mbar_wait(bars + OFF_D_FULL + 8 * s, g & 1u, wctx, 207);
-          if (warp == 4 && lane == 0) RINGRNN_STAMP(g, s == 0 ? 5 : 7);
-          tcgen05_fence_after();
-          if (s == 0) freed.early(c, g, 208);
-          // Last step of a tile: nothing is published, and the next tile's first operand comes by TMA, so its MMAs
-          // wait for nothing but this accumulator.  The step's "free" phases must be consumed BEFORE the accumulator
-          // is handed back, or the barrier could complete another phase first and the parity wait below would
-          // never return.  (They complete together with this accumulator, give or take the skew between the CTAs.)
-          if (s == 1 && t + 1 == T) freed.end_of_step(c, g, 208);
-          uint32_t yo[32], yl[32], yr[32];
-          const uint32_t col = tmem_base + lane_base + s * 256 + 32 * h;
-          if (s == 0) {
-            uint32_t sraw;
-            tmem_ld1(tmem_base + lane_base + SUM_COL, &sraw);  // row sum of r_{t-1}
-            tmem_ld32(col, yo);
-            tmem_ld32(col + 64, yl);
-            tmem_ld32(col + 128, yr);
-            tmem_ld_wait();
-            c0 = J0 * __uint_as_float(sraw);
+          // The pre-activation of this thread's 32 neurons of sub-slice s.  Two active columns: one accumulator holds
+          // the three products, mixed inside the activation loop below (yo, yl, yr).  Weight groups: one accumulator
+          // per group, summed here into re_all.
+          uint32_t yo[GEN ? 1 : 32], yl[GEN ? 1 : 32], yr[GEN ? 1 : 32];
+          float re_all[GEN ? 32 : 1];
+          if constexpr (!GEN) {
+            mbar_wait(bars + OFF_D_FULL + 8 * s, g & 1u, wctx, 207);
+            if (warp == 4 && lane == 0) RINGRNN_STAMP(g, s == 0 ? 5 : 7);
+            tcgen05_fence_after();
+            if (s == 0) freed.early(c, g, 208);
+            // Last step of a tile: nothing is published, and the next tile's first operand comes by TMA, so its MMAs
+            // wait for nothing but this accumulator.  The step's "free" phases must be consumed BEFORE the accumulator
+            // is handed back, or the barrier could complete another phase first and the parity wait below would
+            // never return.  (They complete together with this accumulator, give or take the skew between the CTAs.)
+            if (s == 1 && t + 1 == T) freed.end_of_step(c, g, 208);
+            const uint32_t col = tmem_base + lane_base + s * 256 + 32 * h;
+            if (s == 0) {
+              uint32_t sraw;
+              tmem_ld1(tmem_base + lane_base + SUM_COL, &sraw);  // row sum of r_{t-1}
+              tmem_ld32(col, yo);
+              tmem_ld32(col + 64, yl);
+              tmem_ld32(col + 128, yr);
+              tmem_ld_wait();
+              c0 = J0 * __uint_as_float(sraw);
+            } else {
+              tmem_ld32(col, yo);
+              tmem_ld32(col + 64, yl);
+              tmem_ld32(col + 128, yr);
+              tmem_ld_wait();
+            }
+            release_accumulator<NP, PAIR>(c, s, lane);  // the accumulator is in registers: hand it back
           } else {
-            tmem_ld32(col, yo);
-            tmem_ld32(col + 64, yl);
-            tmem_ld32(col + 128, yr);
-            tmem_ld_wait();
+            for (int grp = 0; grp < ng; ++grp) {
+              // coefficients of the group's three matrices: J1 for Wo, the action scalar for an action matrix
+              float k0, k1 = 0.f, k2 = 0.f;
+              {
+                const int i0 = 3 * grp - 1;  // index into cols[] of the group's first matrix (-1: Wo)
+                k0 = (grp == 0) ? J1 : ((valid && i0 < p.n_act) ? __ldg(at + p.cols[i0]) : 0.f);
+                if (valid && i0 + 1 < p.n_act) k1 = __ldg(at + p.cols[i0 + 1]);
+                if (valid && i0 + 2 < p.n_act) k2 = __ldg(at + p.cols[i0 + 2]);
+              }
+              const uint32_t pass = (g * 2u + (uint32_t)s) * (uint32_t)ng + (uint32_t)grp, acc = pass & 1u;
+              mbar_wait(bars + OFF_D_FULL + 8 * acc, (pass >> 1) & 1u, wctx, 207);
+              tcgen05_fence_after();
+              // last pass of the last step of a tile: see the comment in the two-column branch
+              if (s == 1 && grp == ng - 1 && t + 1 == T) freed.end_of_step(c, g, 208);
+              const uint32_t col = tmem_base + lane_base + acc * 256 + 32 * h;
+              if (s == 0 && grp == 0) {
+                uint32_t sraw;
+                tmem_ld1(tmem_base + lane_base + acc * 256 + SUM_COL, &sraw);  // row sum of r_{t-1}
+                tmem_ld_wait();
+                c0 = J0 * __uint_as_float(sraw);
+              }
+#pragma unroll
+              for (int c16 = 0; c16 < 2; ++c16) {
+                uint32_t z0[16], z1[16], z2[16];
+                tmem_ld16(col + 16 * c16, z0);
+                tmem_ld16(col + 64 + 16 * c16, z1);
+                tmem_ld16(col + 128 + 16 * c16, z2);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  float v = (grp == 0) ? c0 : re_all[16 * c16 + j];
+                  v = fmaf(k0, __uint_as_float(z0[j]), v);
+                  v = fmaf(k1, __uint_as_float(z1[j]), v);
+                  re_all[16 * c16 + j] = fmaf(k2, __uint_as_float(z2[j]), v);
+                }
+              }
+              release_accumulator<NP, PAIR>(c, (int)acc, lane);
+            }
           }
-          release_accumulator<NP, PAIR>(c, s, lane);  // the accumulator is in registers: hand it back
           if (warp == 4 && lane == 0) RINGRNN_STAMP(g, s == 0 ? 6 : 8);
           uint32_t dpk[16], pos = 0u, neg = 0u;
 #pragma unroll
@@ -125,9 +174,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             float re[8], f[8], d[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-              float v = fmaf(J1, __uint_as_float(yo[j0 + e]), c0);
-              v = fmaf(L, __uint_as_float(yl[j0 + e]), v);
-              re[e] = fmaf(R, __uint_as_float(yr[j0 + e]), v);
+              if constexpr (GEN) {
+                re[e] = re_all[j0 + e];
+              } else {
+                float v = fmaf(J1, __uint_as_float(yo[j0 + e]), c0);
+                v = fmaf(L, __uint_as_float(yl[j0 + e]), v);
+                re[e] = fmaf(R, __uint_as_float(yr[j0 + e]), v);
+              }
             }
             act_group<ACT, 8>(re, f, d);
 #pragma unroll
@@ -212,10 +265,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   teardown_cta<NP, PAIR>(c);
 }
 
-template <int ACT, int NP, bool PAIR>
+template <int ACT, int NP, bool PAIR, bool GEN = false>
 static int launch_fwd_tc(const CUtensorMap& tmW, const CUtensorMap& tmR0, const TcFwdParams& p, cudaStream_t s) {
   using C_ = Cfg<NP, PAIR>;
-  auto kernel = fwd_tc_kernel<ACT, NP, PAIR>;
+  auto kernel = fwd_tc_kernel<ACT, NP, PAIR, GEN>;
   RINGRNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM));
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -240,6 +293,17 @@ static int launch_fwd_tc(const CUtensorMap& tmW, const CUtensorMap& tmR0, const 
 
 int tc_forward_launch(int act, int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmR0, const TcFwdParams& p,
                       cudaStream_t s) {
+  if (p.ng > 1) {  // more than two active action columns
+    if (pair) return RINGRNN_ERR_UNSUPPORTED;
+#define RINGRNN_TCG(ACT, NPV) \
+  if (act == ACT && NP == NPV) return launch_fwd_tc<ACT, NPV, false, true>(tmW, tmR0, p, s);
+    RINGRNN_TCG(RINGRNN_ACT_RELU, 128) RINGRNN_TCG(RINGRNN_ACT_RELU, 256) RINGRNN_TCG(RINGRNN_ACT_RELU, 512)
+    RINGRNN_TCG(RINGRNN_ACT_GELU, 128) RINGRNN_TCG(RINGRNN_ACT_GELU, 256) RINGRNN_TCG(RINGRNN_ACT_GELU, 512)
+    RINGRNN_TCG(RINGRNN_ACT_TANH, 128) RINGRNN_TCG(RINGRNN_ACT_TANH, 256) RINGRNN_TCG(RINGRNN_ACT_TANH, 512)
+    RINGRNN_TCG(RINGRNN_ACT_SILU, 128) RINGRNN_TCG(RINGRNN_ACT_SILU, 256) RINGRNN_TCG(RINGRNN_ACT_SILU, 512)
+#undef RINGRNN_TCG
+    return RINGRNN_ERR_UNSUPPORTED;
+  }
 #define RINGRNN_TCF(ACT, NPV)                                                              \
   if (act == ACT && NP == NPV)                                                             \
     return pair ? launch_fwd_tc<ACT, NPV, true>(tmW, tmR0, p, s) : launch_fwd_tc<ACT, NPV, false>(tmW, tmR0, p, s);

@@ -73,6 +73,10 @@ struct TcFwdParams {
   const float* dec_v;
   float* final_state;    // [B,N] or nullptr
   int* status;
+  // generic action columns (more than two active): the weight blocks come in `ng` groups of three matrices,
+  // group 0 = {Wo, Wa[cols[0]], Wa[cols[1]]} + ones row, group m = {Wa[cols[3m-1]], Wa[cols[3m]], Wa[cols[3m+1]]}
+  int ng, n_act;
+  int cols[RINGRNN_MAX_ACTIVE];
 };
 
 struct TcBwdParams {
@@ -90,10 +94,14 @@ struct TcBwdParams {
   __nv_bfloat16* DL;            // [T*BP][3*NP]
   float* grad_r_init;           // [B,N] or nullptr
   const __nv_bfloat16* Rh;      // [T+1][BP][NP] saved state (read only when dA_part is set)
-  float* dA_part;               // [2C][2][T][BP] partial sums of dL/dL_t and dL/dR_t, or nullptr
+  float* dA_part;               // [2C][2][T][BP] partial sums of dL/dL_t and dL/dR_t (generic columns:
+                                // [4C][n_act][T][BP]), or nullptr
   int* status;
+  int ng, n_act;                // as in TcFwdParams; DL then has 1 + n_act column blocks [delta | A_k * delta ...]
+  int cols[RINGRNN_MAX_ACTIVE];
 };
 
+// `generic`: more than two active action columns (p.ng > 1 weight groups); NP <= 512, no CTA pairs
 int tc_forward_launch(int act, int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmR0, const TcFwdParams& p,
                       cudaStream_t s);
 int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmDL, const TcBwdParams& p,
@@ -320,11 +328,11 @@ __device__ __forceinline__ void teardown_cta(const Ctx<NP, PAIR>& c) {
   }
 }
 
-// Weight stream (one thread per CTA).  Tile order per step: round by round, sub-slice 0 then 1, the slots starting at
-// this slice's own.
+// Weight stream (one thread per CTA).  Tile order per step: round by round, sub-slice 0 then 1, within a sub-slice
+// the `ng` weight groups one after the other, the slots starting at this slice's own.
 template <int NP, bool PAIR>
 __device__ __forceinline__ void producer_loop(const Ctx<NP, PAIR>& c, const CUtensorMap* tmW, uint32_t total_steps,
-                                              int code) {
+                                              int code, int ng = 1) {
   using C_ = Cfg<NP, PAIR>;
   using namespace tc;
   constexpr int KC = C_::KC, NS = C_::NS, SL = C_::SLOTS, R = C_::ROUNDS;
@@ -332,28 +340,29 @@ __device__ __forceinline__ void producer_loop(const Ctx<NP, PAIR>& c, const CUte
   if (total_steps == 0) return;
   const uint64_t keep = l2_policy_evict_last();
   const int rot = (2 * c.q) % SL;
-  auto issue = [&](int st, int s, int kc) {
+  auto issue = [&](int st, int s, int grp, int kc) {
     const uint32_t bar = c.bars + OFF_W_FULL + 8 * st;
-    const int y = (c.q * 2 + s) * C_::RB + c.half * C_::WROWS;
+    const int y = ((c.q * 2 + s) * ng + grp) * C_::RB + c.half * C_::WROWS;
     if (c.leader) mbar_arrive_expect_tx(bar, (PAIR ? 2 : 1) * C_::WT_BYTES);  // a pair's two halves land on one barrier
     if (PAIR) tma_load_2d_pair(c.w_base + st * C_::WT_BYTES, tmW, bar, kc * 64, y);
     else tma_load_2d_hint(c.w_base + st * C_::WT_BYTES, tmW, bar, kc * 64, y, keep);
   };
-  if (C_::RESIDENT) {
+  if (C_::RESIDENT && ng == 1) {
     for (int s = 0; s < 2; ++s)
-      for (int i = 0; i < KC; ++i) issue(s * KC + i, s, (rot + i) % SL);
+      for (int i = 0; i < KC; ++i) issue(s * KC + i, s, 0, (rot + i) % SL);
   } else {
     uint32_t wcount = 0;
     for (uint32_t g = 0; g < total_steps; ++g)
       for (int round = 0; round < R; ++round)
         for (int s = 0; s < 2; ++s)
-          for (int i = 0; i < SL; ++i, ++wcount) {
-            const int st = wcount % NS;
-            if (wcount >= (uint32_t)NS &&
-                !mbar_wait(c.bars + OFF_W_EMPTY + 8 * st, (wcount / NS - 1) & 1u, c.wctx, code))
-              return;  // abandoned: issue nothing more
-            issue(st, s, round * SL + (rot + i) % SL);
-          }
+          for (int grp = 0; grp < ng; ++grp)
+            for (int i = 0; i < SL; ++i, ++wcount) {
+              const int st = wcount % NS;
+              if (wcount >= (uint32_t)NS &&
+                  !mbar_wait(c.bars + OFF_W_EMPTY + 8 * st, (wcount / NS - 1) & 1u, c.wctx, code))
+                return;  // abandoned: issue nothing more
+              issue(st, s, grp, round * SL + (rot + i) % SL);
+            }
   }
 }
 
@@ -363,7 +372,8 @@ __device__ __forceinline__ void producer_loop(const Ctx<NP, PAIR>& c, const CUte
 // MMA issuer (one thread of the leader CTA).  `stores`: the epilogue publishes this CTA's chunks with a TMA store
 // (only looked at with two K rounds, where a peer overwrites the slots of this CTA's own chunks in the other round).
 template <int NP, bool PAIR, bool FWD>
-__device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_steps, int T, int code, bool stores) {
+__device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_steps, int T, int code, bool stores,
+                                         int ng = 1) {
   using C_ = Cfg<NP, PAIR>;
   using namespace tc;
   constexpr int KC = C_::KC, NS = C_::NS, SL = C_::SLOTS, R = C_::ROUNDS;
@@ -390,61 +400,70 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
       const int next_round = (round + 1) % R;
       const int next_t = (round + 1 < R) ? t : (t + 1 == T ? 0 : t + 1);
       const bool next_by_copy = FWD ? (next_t != 0) : (ph + 1 < total_steps * (uint32_t)R);
+      // A pass = all K chunks of this round into one accumulator: (sub-slice s, weight group grp).  Passes take
+      // the two accumulators in turn: pass number n uses accumulator n & 1 for the (n >> 1)-th time.  (With two K
+      // rounds there is one group, and both rounds of a sub-slice go into the same accumulator.)
+      const bool resident = C_::RESIDENT && ng == 1;
       for (int s = 0; s < 2; ++s) {
-        if (round == 0) {
-          if (g > 0 && !mbar_wait<PAIR>(c.bars + OFF_D_EMPTY + 8 * s, (g - 1) & 1u, c.wctx, code + 0)) return;
-          RINGRNN_STAMP(g, s == 0 ? 0 : 2);
-        }
-        tcgen05_fence_after();
-        for (int i = 0; i < SL; ++i) {
-          const int slot = (rot + i) % SL;
-          if (s == 0) {
-#ifdef RINGRNN_TIMELINE
-            t0 = clock64();
-#endif
-            if (!mbar_wait(c.bars + OFF_A_FULL + 8 * slot, ph & 1u, c.wctx, code + 1)) return;
-#ifdef RINGRNN_TIMELINE
-            acc_a += clock64() - t0;
-            t0 = clock64();
-#endif
-            if (next_by_copy && ((next_round * SL + slot) >> 1) != c.q)
-              mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * slot, CHUNK_BYTES);
-            if (PAIR && !mbar_wait<true>(c.bars + OFF_A_PAIR + 8 * slot, g & 1u, c.wctx, code + 2)) return;
-#ifdef RINGRNN_TIMELINE
-            acc_p += clock64() - t0;
-            if (i == 1 && round == 0) RINGRNN_STAMP(g, 1);
-#endif
-          }
-          int st;
-          if (C_::RESIDENT) {
-            st = s * KC + i;
-            if (g == 0 && !mbar_wait(c.bars + OFF_W_FULL + 8 * st, 0, c.wctx, code + 3)) return;
-          } else {
-            st = wcount % NS;
-#ifdef RINGRNN_TIMELINE
-            t0 = clock64();
-#endif
-            if (!mbar_wait(c.bars + OFF_W_FULL + 8 * st, (wcount / NS) & 1u, c.wctx, code + 3)) return;
-#ifdef RINGRNN_TIMELINE
-            acc_w += clock64() - t0;
-#endif
+        for (int grp = 0; grp < ng; ++grp) {
+          const uint32_t pass = (g * 2u + (uint32_t)s) * (uint32_t)ng + (uint32_t)grp;
+          const uint32_t acc = pass & 1u;
+          if (round == 0) {
+            if (pass >= 2 && !mbar_wait<PAIR>(c.bars + OFF_D_EMPTY + 8 * acc, ((pass >> 1) - 1) & 1u, c.wctx, code + 0))
+              return;
+            if (grp == 0) RINGRNN_STAMP(g, s == 0 ? 0 : 2);
           }
           tcgen05_fence_after();
-          const uint32_t a_lo = desc_lo(c.a_base + slot * CHUNK_BYTES, 16), b_lo = desc_lo(c.w_base + st * C_::WT_BYTES, 16);
+          for (int i = 0; i < SL; ++i) {
+            const int slot = (rot + i) % SL;
+            if (s == 0 && grp == 0) {
+#ifdef RINGRNN_TIMELINE
+              t0 = clock64();
+#endif
+              if (!mbar_wait(c.bars + OFF_A_FULL + 8 * slot, ph & 1u, c.wctx, code + 1)) return;
+#ifdef RINGRNN_TIMELINE
+              acc_a += clock64() - t0;
+              t0 = clock64();
+#endif
+              if (next_by_copy && ((next_round * SL + slot) >> 1) != c.q)
+                mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * slot, CHUNK_BYTES);
+              if (PAIR && !mbar_wait<true>(c.bars + OFF_A_PAIR + 8 * slot, g & 1u, c.wctx, code + 2)) return;
+#ifdef RINGRNN_TIMELINE
+              acc_p += clock64() - t0;
+              if (i == 1 && round == 0) RINGRNN_STAMP(g, 1);
+#endif
+            }
+            int st;
+            if (resident) {
+              st = s * KC + i;
+              if (g == 0 && !mbar_wait(c.bars + OFF_W_FULL + 8 * st, 0, c.wctx, code + 3)) return;
+            } else {
+              st = wcount % NS;
+#ifdef RINGRNN_TIMELINE
+              t0 = clock64();
+#endif
+              if (!mbar_wait(c.bars + OFF_W_FULL + 8 * st, (wcount / NS) & 1u, c.wctx, code + 3)) return;
+#ifdef RINGRNN_TIMELINE
+              acc_w += clock64() - t0;
+#endif
+            }
+            tcgen05_fence_after();
+            const uint32_t a_lo = desc_lo(c.a_base + slot * CHUNK_BYTES, 16), b_lo = desc_lo(c.w_base + st * C_::WT_BYTES, 16);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const uint32_t acc = (round > 0 || i > 0 || ks > 0) ? 1u : 0u;
-            if (PAIR) umma_ss_pair_lo(c.tmem_base + s * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc, acc);
-            else umma_ss_lo(c.tmem_base + s * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc, acc);
+            for (int ks = 0; ks < 4; ++ks) {
+              const uint32_t accum = (round > 0 || i > 0 || ks > 0) ? 1u : 0u;
+              if (PAIR) umma_ss_pair_lo(c.tmem_base + acc * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc, accum);
+              else umma_ss_lo(c.tmem_base + acc * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc, accum);
+            }
+            if (!resident) {
+              commit(c.bars + OFF_W_EMPTY + 8 * st);
+              ++wcount;
+            }
           }
-          if (!C_::RESIDENT) {
-            commit(c.bars + OFF_W_EMPTY + 8 * st);
-            ++wcount;
+          if (round == R - 1) {
+            commit(c.bars + OFF_D_FULL + 8 * acc);
+            if (grp == ng - 1) RINGRNN_STAMP(g, s == 0 ? 3 : 4);
           }
-        }
-        if (round == R - 1) {
-          commit(c.bars + OFF_D_FULL + 8 * s);
-          RINGRNN_STAMP(g, s == 0 ? 3 : 4);
         }
       }
       if (R > 1 && round == rq && stores && (!FWD || t != 0)) {

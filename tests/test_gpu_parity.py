@@ -50,7 +50,11 @@ FWD_SHAPES = [
     (120, 130, 65, 2, "gelu", False),
     (128, 128, 65, 2, "silu", False),
     (256, 130, 20, 16, "gelu", True),    # zero-padded action columns, as the root training script
-    (40, 33, 17, 4, "relu", False),      # generic action columns
+    (40, 33, 17, 4, "silu", False),      # generic action columns: two weight groups in bf16 mode
+    (128, 40, 6, 5, "tanh", False),      # six matrices = two full groups
+    (512, 130, 5, 16, "gelu", False),    # a_dim 16, as in the reference's published latency table: six groups
+    (256, 200, 4, 7, "silu", False),
+    (100, 19300, 3, 3, "tanh", False),   # weight groups with several tiles per cluster (weights not resident)
     (256, 7, 9, 2, "tanh", False),
     (512, 16, 5, 2, "gelu", False),
     (512, 260, 6, 2, "gelu", False),     # CTA pairs, cluster of 8, two 256-sample tiles (one mostly padding)
