@@ -247,6 +247,61 @@ def run_rollout(args, wl):
     print(json.dumps(line), flush=True)
 
 
+# The reference's own published table (assets/REPORT.md, RTX PRO 6000 Blackwell, forward op latency at B=256, T=20):
+# (N, a_dim, "CUDA" fp32 kernel ms, "CUDA WMMA" ms or None)
+PUBLISHED_FORWARD_MS = [
+    (128, 16, 0.372, 0.282), (256, 16, 0.897, 0.595), (384, 16, 1.755, 1.269), (512, 16, 2.795, 1.772),
+    (1024, 16, 10.172, 6.163), (2048, 16, 46.110, 24.455), (2048, 32, 76.646, 36.741), (2048, 64, 139.247, 62.792),
+    (1024, 2, 10.112, None), (1024, 3, 10.129, None), (1024, 6, 10.744, None), (1024, 12, 10.549, None),
+]
+
+
+def run_published_table(args):
+    """Forward op latency on the shapes of the reference's published table, measured the way the reference measures
+    (utils/benchmark.py:58-79: 2 warm-up calls, then 20 calls each bracketed by CUDA events and a synchronize), through
+    the reference's own entry point ring_rnn_cuda_func.  Action signal as legacy/model_fp32.py:116-124
+    (relu(av * linspace(-1, 1, a_dim))): every column is active somewhere in the batch.  One JSON line."""
+    from rnn_train_ring_attractor_b200.build import build
+    from rnn_train_ring_attractor_b200.inputs import generate_av, initial_bump_von_mises
+    from rnn_train_ring_attractor_b200.ring_rnn_cuda import ring_rnn_cuda_func, set_precision
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    build()
+    B, T = 256, 20
+    rows = []
+    for N, a_dim, ref_fp32_ms, ref_wmma_ms in PUBLISHED_FORWARD_MS:
+        g = torch.Generator().manual_seed(N + a_dim)
+        av, angle = generate_av(B, T, generator=g)
+        A = torch.relu(av.unsqueeze(-1) * torch.linspace(-1, 1, a_dim)).contiguous().to(dev)
+        Wa = (torch.randn(a_dim, N, N, generator=g) / math.sqrt(N)).to(dev)
+        Wo = (torch.randn(N, N, generator=g) / math.sqrt(N)).to(dev)
+        r0 = initial_bump_von_mises(angle[:, 0], N).to(dev)
+        row = {"N": N, "a_dim": a_dim, "reference_fp32_ms": ref_fp32_ms, "reference_wmma_ms": ref_wmma_ms}
+        # the fp32 parity mode is timed on the smaller shapes only (seconds per call at N = 2048)
+        for mode in (("auto", "fp32") if N <= 512 else ("auto",)):
+            set_precision(mode)
+            with torch.no_grad():
+                for _ in range(2):
+                    ring_rnn_cuda_func(A, Wa, -0.1, 0.1, Wo, r0, 0.15, "tanh")
+                torch.cuda.synchronize()
+                times = []
+                for _ in range(20):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    ring_rnn_cuda_func(A, Wa, -0.1, 0.1, Wo, r0, 0.15, "tanh")
+                    e1.record()
+                    torch.cuda.synchronize()
+                    times.append(e0.elapsed_time(e1))
+            tt = torch.tensor(times)
+            row["ms_" + mode] = float(tt.mean())
+            row["std_" + mode] = float(tt.std(unbiased=False))
+        set_precision("auto")
+        rows.append(row)
+    print(json.dumps({"metric": "forward op latency on the reference's published shapes", "unit": "ms", "B": B, "T": T,
+                      "reference_hardware": "RTX PRO 6000 Blackwell (published, other hardware)", "rows": rows}),
+          flush=True)
+
+
 def run_ours(args, wl):
     import torch.distributed as dist
     from rnn_train_ring_attractor_b200 import _lib, dp
@@ -412,13 +467,16 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + ["published"])
     ap.add_argument("--precision", default="auto", choices=["auto", "bf16", "fp32"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--seq-len", type=int, default=0, help="override T (profiling on a smaller case of the same kernels)")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling)")
     args = ap.parse_args()
+    if args.workload == "published":
+        run_published_table(args)
+        return
     wl = dict(WORKLOADS[args.workload])
     if args.seq_len:
         wl["T"] = args.seq_len

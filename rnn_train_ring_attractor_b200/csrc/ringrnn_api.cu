@@ -109,7 +109,16 @@ extern "C" const char* ringrnn_last_cuda_error_string(void) { return cudaGetErro
 extern "C" size_t ringrnn_workspace_bytes(const RingRnnProblem* p, int which, int history_given) {
   if (p == nullptr || check_problem(*p) != RINGRNN_OK) return (size_t)-1;
   const bool bf16 = p->precision == RINGRNN_PREC_BF16;
-  if (bf16 && !bf16_supported(*p)) return (size_t)-1;
+  if (bf16 && !bf16_supported(*p)) {
+    // bf16 arithmetic, one GEMM per timestep: the shapes the persistent kernels do not take
+    if (!stepwise_supported(*p)) return (size_t)-1;
+    switch (which) {
+      case RINGRNN_WS_FWD: return stepwise_fwd_workspace_bytes(*p);
+      case RINGRNN_WS_SAVED: return stepwise_saved_bytes(*p);
+      case RINGRNN_WS_BWD: return stepwise_bwd_workspace_bytes(*p);
+      default: return (size_t)-1;
+    }
+  }
   switch (which) {
     case RINGRNN_WS_FWD: return bf16 ? bf16_fwd_workspace_bytes(*p) : fp32_fwd_workspace_bytes(*p);
     case RINGRNN_WS_SAVED: return bf16 ? bf16_saved_bytes(*p) : fp32_saved_bytes(*p, history_given);
@@ -130,8 +139,9 @@ extern "C" int ringrnn_fwd(const RingRnnFwdArgs* a, void* stream) {
   const DevProblem dp = to_dev(a->p);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (a->p.precision == RINGRNN_PREC_BF16) {
-    if (!bf16_supported(a->p)) return RINGRNN_ERR_UNSUPPORTED;
-    return bf16_forward(*a, dp, s);
+    if (bf16_supported(a->p)) return bf16_forward(*a, dp, s);
+    if (stepwise_supported(a->p)) return stepwise_forward(*a, dp, s);
+    return RINGRNN_ERR_UNSUPPORTED;
   }
   return fp32_forward(*a, dp, s);
 }
@@ -148,8 +158,9 @@ extern "C" int ringrnn_bwd(const RingRnnBwdArgs* a, void* stream) {
   const DevProblem dp = to_dev(a->p);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (a->p.precision == RINGRNN_PREC_BF16) {
-    if (!bf16_supported(a->p)) return RINGRNN_ERR_UNSUPPORTED;
-    return bf16_backward(*a, dp, s);
+    if (bf16_supported(a->p)) return bf16_backward(*a, dp, s);
+    if (stepwise_supported(a->p)) return stepwise_backward(*a, dp, s);
+    return RINGRNN_ERR_UNSUPPORTED;
   }
   return fp32_backward(*a, dp, s);
 }

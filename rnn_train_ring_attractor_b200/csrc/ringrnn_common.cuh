@@ -108,4 +108,13 @@ size_t bf16_bwd_workspace_bytes(const RingRnnProblem& p);
 int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s);
 int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s);
 
+// bf16 stepwise path: one tensor-core GEMM per timestep (ringrnn_stepwise.cu), for the shapes the persistent
+// kernels do not take
+bool stepwise_supported(const RingRnnProblem& p);
+size_t stepwise_fwd_workspace_bytes(const RingRnnProblem& p);
+size_t stepwise_saved_bytes(const RingRnnProblem& p);
+size_t stepwise_bwd_workspace_bytes(const RingRnnProblem& p);
+int stepwise_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s);
+int stepwise_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s);
+
 }  // namespace ringrnn

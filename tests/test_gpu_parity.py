@@ -55,6 +55,10 @@ FWD_SHAPES = [
     (512, 130, 5, 16, "gelu", False),    # a_dim 16, as in the reference's published latency table: six groups
     (256, 200, 4, 7, "silu", False),
     (100, 19300, 3, 3, "tanh", False),   # weight groups with several tiles per cluster (weights not resident)
+    # beyond the persistent kernels: bf16 mode runs one tensor-core GEMM per timestep
+    (1024, 130, 4, 5, "tanh", False),    # N = 1024 with more than two active columns
+    (1152, 40, 3, 2, "gelu", False),     # N > 1024, not a multiple of 256
+    (2048, 64, 3, 4, "silu", False),
     (256, 7, 9, 2, "tanh", False),
     (512, 16, 5, 2, "gelu", False),
     (512, 260, 6, 2, "gelu", False),     # CTA pairs, cluster of 8, two 256-sample tiles (one mostly padding)
@@ -189,7 +193,7 @@ def test_autograd_surface_against_reference_training_gradients(name):
 # in dWo at T=32 and any two precisions decorrelate at T=512 -- so that shape is compared at T=8, where errors are
 # still those of the arithmetic; (256, 192, 32) and (512, 192, 32, tanh) cover the longer horizon.
 FUSED_CASES = [(120, 128, 120, "tanh"), (24, 5, 12, "gelu"), (256, 64, 40, "relu"), (512, 192, 8, "gelu"),
-               (256, 192, 32, "gelu"), (512, 192, 32, "tanh"), (1024, 192, 12, "tanh")]
+               (256, 192, 32, "gelu"), (512, 192, 32, "tanh"), (1024, 192, 12, "tanh"), (1280, 40, 5, "tanh")]
 
 
 @pytest.mark.parametrize("cfg", FUSED_CASES, ids=lambda c: "N%d-B%d-T%d-%s" % c)
