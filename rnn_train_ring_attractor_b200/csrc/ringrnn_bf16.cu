@@ -120,10 +120,20 @@ Layout layout_of(const RingRnnProblem& p) {
 
 }  // namespace
 
-// N <= 1024 with up to two active action columns; N <= 512 with up to RINGRNN_MAX_ACTIVE of them
+// Which bf16 requests the persistent kernels take: N <= 1024 with up to two active action columns; N <= 512 with up to
+// RINGRNN_MAX_ACTIVE of them when the batch is large.  A persistent kernel keeps one cluster busy per 128 samples and
+// its step time grows with the number of weight groups, so with more than two columns and at most 1024 samples the
+// stepwise path (one full-machine GEMM per step, ringrnn_stepwise.cu) is faster (measured on the shapes of the
+// reference's published table, B = 256: 0.53 / 0.57 / 0.79 ms against 0.81 / 0.99 / 0.98 ms at N = 256 / 384 / 512),
+// while at B = 4096 the persistent kernels win several times over.
+// RINGRNN_STEPWISE=1 sends every bf16 request to the stepwise path (for comparisons).
 bool bf16_supported(const RingRnnProblem& p) {
+  static const bool force_stepwise = getenv("RINGRNN_STEPWISE") != nullptr && getenv("RINGRNN_STEPWISE")[0] == '1';
+  if (force_stepwise) return false;
   const int NP = padded_n(p.N), n_act = n_active_of(p);
-  return NP != 0 && p.B >= 1 && p.T >= 1 && (n_act <= 2 || (NP <= 512 && n_act <= RINGRNN_MAX_ACTIVE));
+  if (NP == 0 || p.B < 1 || p.T < 1) return false;
+  if (n_act <= 2) return true;
+  return NP <= 512 && n_act <= RINGRNN_MAX_ACTIVE && p.B > 1024;
 }
 
 // FWD workspace: status(1024) | Wf | R0 | dec partials

@@ -50,11 +50,15 @@ FWD_SHAPES = [
     (120, 130, 65, 2, "gelu", False),
     (128, 128, 65, 2, "silu", False),
     (256, 130, 20, 16, "gelu", True),    # zero-padded action columns, as the root training script
-    (40, 33, 17, 4, "silu", False),      # generic action columns: two weight groups in bf16 mode
-    (128, 40, 6, 5, "tanh", False),      # six matrices = two full groups
-    (512, 130, 5, 16, "gelu", False),    # a_dim 16, as in the reference's published latency table: six groups
-    (256, 200, 4, 7, "silu", False),
+    # more than two active action columns, large batch: persistent kernels with weight groups of three matrices
+    (256, 1100, 3, 5, "silu", False),    # six matrices = two full groups
+    (512, 1030, 3, 16, "gelu", False),   # a_dim 16 as in the reference's published latency table: six groups
     (100, 19300, 3, 3, "tanh", False),   # weight groups with several tiles per cluster (weights not resident)
+    # more than two active action columns, small batch: one tensor-core GEMM per timestep
+    (40, 33, 17, 4, "silu", False),
+    (128, 40, 6, 5, "tanh", False),
+    (512, 130, 5, 16, "gelu", False),
+    (256, 200, 4, 7, "silu", False),
     # beyond the persistent kernels: bf16 mode runs one tensor-core GEMM per timestep
     (1024, 130, 4, 5, "tanh", False),    # N = 1024 with more than two active columns
     (1152, 40, 3, 2, "gelu", False),     # N > 1024, not a multiple of 256
