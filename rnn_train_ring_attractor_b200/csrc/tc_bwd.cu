@@ -42,16 +42,16 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   const uint32_t total_steps = (uint32_t)my_tiles * (uint32_t)T;
 
   if (warp < 4) {
-    reg_dec<40>();
+    reg_dec<LOW_REGS>();
     if (warp == 0 && lane == 0) {
-      producer_loop<NP, PAIR>(c, &tmW, total_steps, 302, ng);
+      producer_loop<NP, PAIR, GEN>(c, &tmW, total_steps, 302, ng);
     } else if (warp == 1 && lane == 0) {
-      if (c.leader) mma_loop<NP, PAIR, false>(c, total_steps, T, 310, true, ng);
+      if (c.leader) mma_loop<NP, PAIR, false, GEN>(c, total_steps, T, 310, true, ng);
     } else if (warp == 2 && lane == 0) {
       relay_loop<NP, PAIR, false>(c, total_steps, T, 320, [](int, int) {});
     }
   } else {
-    reg_inc<232>();
+    reg_inc<HIGH_REGS>();
     // ---------------- epilogue: thread = sample.  Warps 4-7 (h = 0) own columns [0,32) and warps 8-11 (h = 1)
     // columns [32,64) of both 64-neuron sub-slices; master[s*32 + j] is neuron 128q + 64s + 32h + j. ----------------
     const int h = (warp - 4) >> 2, quarter = warp & 3;

@@ -39,11 +39,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   const uint32_t total_steps = (uint32_t)my_tiles * (uint32_t)T;
 
   if (warp < 4) {
-    reg_dec<40>();
+    reg_dec<LOW_REGS>();
     if (warp == 0 && lane == 0) {
-      producer_loop<NP, PAIR>(c, &tmW, total_steps, 202, ng);
+      producer_loop<NP, PAIR, GEN>(c, &tmW, total_steps, 202, ng);
     } else if (warp == 1 && lane == 0) {
-      if (c.leader) mma_loop<NP, PAIR, true>(c, total_steps, T, 210, p.Rh != nullptr, ng);
+      if (c.leader) mma_loop<NP, PAIR, true, GEN>(c, total_steps, T, 210, p.Rh != nullptr, ng);
     } else if (warp == 2 && lane == 0) {
       tma_prefetch_desc(&tmR0);
       relay_loop<NP, PAIR, true>(c, total_steps, T, 220, [&](int it, int round) {
@@ -58,7 +58,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       });
     }
   } else {
-    reg_inc<232>();
+    reg_inc<HIGH_REGS>();
     // ---------------- epilogue: thread = sample.  Warps 4-7 (h = 0) own columns [0,32) and warps 8-11 (h = 1)
     // columns [32,64) of BOTH 64-neuron sub-slices, so every accumulator is drained by all eight warps at once
     // (two warps per scheduler) and the part of the step that nothing overlaps -- the epilogue of the last

@@ -111,6 +111,12 @@ namespace tcr {
 
 constexpr int CHUNK_BYTES = 128 * 128;  // one [128 samples x 64 neurons] bf16 chunk
 constexpr int THREADS = 384;         // warps 0-3: TMA / MMA / relay / idle; warps 4-11: epilogue
+// Register re-distribution (setmaxnreg): the CTA is launched with 168 registers per thread (65536 / 384, rounded down
+// to a multiple of 8); warps 0-3 give theirs back down to LOW_REGS, the epilogue warps grow to HIGH_REGS.  The sum
+// must fit in what the CTA was launched with -- a request beyond that waits for ever, it is not an error.
+constexpr int LOW_REGS = 40, HIGH_REGS = 232;
+static_assert((4 * LOW_REGS + 8 * HIGH_REGS) * 32 <= (65536 / THREADS / 8 * 8) * THREADS,
+              "setmaxnreg budget exceeds the registers the CTA is launched with");
 constexpr int SMEM_LIMIT = 232448;   // 227 KB
 constexpr int TMEM_COLS = 512;
 constexpr int SUM_COL = 192;
@@ -330,10 +336,11 @@ __device__ __forceinline__ void teardown_cta(const Ctx<NP, PAIR>& c) {
 
 // Weight stream (one thread per CTA).  Tile order per step: round by round, sub-slice 0 then 1, within a sub-slice
 // the `ng` weight groups one after the other, the slots starting at this slice's own.
-template <int NP, bool PAIR>
+template <int NP, bool PAIR, bool GEN = false>
 __device__ __forceinline__ void producer_loop(const Ctx<NP, PAIR>& c, const CUtensorMap* tmW, uint32_t total_steps,
-                                              int code, int ng = 1) {
+                                              int code, int ng_arg = 1) {
   using C_ = Cfg<NP, PAIR>;
+  const int ng = GEN ? ng_arg : 1;  // a compile-time 1 for the two-column kernels
   using namespace tc;
   constexpr int KC = C_::KC, NS = C_::NS, SL = C_::SLOTS, R = C_::ROUNDS;
   tma_prefetch_desc(tmW);
@@ -351,17 +358,21 @@ __device__ __forceinline__ void producer_loop(const Ctx<NP, PAIR>& c, const CUte
     for (int s = 0; s < 2; ++s)
       for (int i = 0; i < KC; ++i) issue(s * KC + i, s, 0, (rot + i) % SL);
   } else {
-    uint32_t wcount = 0;
+    int st = 0;              // ring stage of the next tile
+    uint32_t lap = 0;        // how many times the ring has been filled
     for (uint32_t g = 0; g < total_steps; ++g)
       for (int round = 0; round < R; ++round)
         for (int s = 0; s < 2; ++s)
           for (int grp = 0; grp < ng; ++grp)
-            for (int i = 0; i < SL; ++i, ++wcount) {
-              const int st = wcount % NS;
-              if (wcount >= (uint32_t)NS &&
-                  !mbar_wait(c.bars + OFF_W_EMPTY + 8 * st, (wcount / NS - 1) & 1u, c.wctx, code))
+#pragma unroll 1
+            for (int i = 0; i < SL; ++i) {
+              if (lap > 0 && !mbar_wait(c.bars + OFF_W_EMPTY + 8 * st, (lap - 1) & 1u, c.wctx, code))
                 return;  // abandoned: issue nothing more
               issue(st, s, grp, round * SL + (rot + i) % SL);
+              if (++st == NS) {
+                st = 0;
+                ++lap;
+              }
             }
   }
 }
@@ -371,16 +382,19 @@ __device__ __forceinline__ void producer_loop(const Ctx<NP, PAIR>& c, const CUte
 //
 // MMA issuer (one thread of the leader CTA).  `stores`: the epilogue publishes this CTA's chunks with a TMA store
 // (only looked at with two K rounds, where a peer overwrites the slots of this CTA's own chunks in the other round).
-template <int NP, bool PAIR, bool FWD>
+template <int NP, bool PAIR, bool FWD, bool GEN = false>
 __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_steps, int T, int code, bool stores,
-                                         int ng = 1) {
+                                         int ng_arg = 1) {
   using C_ = Cfg<NP, PAIR>;
+  const int ng = GEN ? ng_arg : 1;  // a compile-time 1 for the two-column kernels
   using namespace tc;
   constexpr int KC = C_::KC, NS = C_::NS, SL = C_::SLOTS, R = C_::ROUNDS;
   constexpr uint32_t idesc = make_idesc_bf16(PAIR ? 256 : 128, C_::RB, 0, 0);
   const int rot = (2 * c.q) % SL, rq = (2 * c.q) / SL;
-  uint32_t wcount = 0, ph = 0, npub = 0;
-  int t = 0;  // step within the tile
+  uint32_t ph = 0, npub = 0;
+  int wst = 0;          // ring stage of the next weight tile
+  uint32_t wpar = 0;    // parity of that stage's current fill
+  int t = 0;            // step within the tile
   if (!FWD && total_steps > 0)  // reverse: nothing loads the first A operand by TMA, peers push it
     for (int slot = 0; slot < SL; ++slot)
       if ((slot >> 1) != c.q) mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * slot, CHUNK_BYTES);
@@ -414,6 +428,9 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
             if (grp == 0) RINGRNN_STAMP(g, s == 0 ? 0 : 2);
           }
           tcgen05_fence_after();
+          // kept rolled: a small loop body keeps this thread within its 40 registers and its instruction footprint
+          // small (the unrolled loop measured slower)
+#pragma unroll 1
           for (int i = 0; i < SL; ++i) {
             const int slot = (rot + i) % SL;
             if (s == 0 && grp == 0) {
@@ -438,11 +455,11 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
               st = s * KC + i;
               if (g == 0 && !mbar_wait(c.bars + OFF_W_FULL + 8 * st, 0, c.wctx, code + 3)) return;
             } else {
-              st = wcount % NS;
+              st = wst;
 #ifdef RINGRNN_TIMELINE
               t0 = clock64();
 #endif
-              if (!mbar_wait(c.bars + OFF_W_FULL + 8 * st, (wcount / NS) & 1u, c.wctx, code + 3)) return;
+              if (!mbar_wait(c.bars + OFF_W_FULL + 8 * st, wpar, c.wctx, code + 3)) return;
 #ifdef RINGRNN_TIMELINE
               acc_w += clock64() - t0;
 #endif
@@ -457,7 +474,10 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
             }
             if (!resident) {
               commit(c.bars + OFF_W_EMPTY + 8 * st);
-              ++wcount;
+              if (++wst == NS) {
+                wst = 0;
+                wpar ^= 1u;
+              }
             }
           }
           if (round == R - 1) {
