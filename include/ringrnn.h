@@ -189,6 +189,17 @@ int ringrnn_angle_loss_static(int B, int T, const float* dec_x, const float* dec
                               const float* target, float bump_weight, float inv_count, float* coef_x,
                               float* coef_y, float* coef_s, float* decoded, float* loss_out, void* stream);
 
+/* Optimizer step on flat buffers, entirely on the device: clip the gradient to a global L2 norm of `max_norm`
+ * (max_norm <= 0: no clipping), then one Adam update (no weight decay, no amsgrad).  Replaces the pair
+ * torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0); optimizer.step() of
+ * train_general_ring_no_gain.py:335-336 for parameters kept in one contiguous fp32 buffer laid out like the
+ * gradient buffer of the data-parallel step ([Wo | Wa | J0 J1]); same arithmetic, no read-back of the norm.
+ *   params, grads, exp_avg, exp_avg_sq   n floats each (grads is not modified)
+ *   step                                 1 for the first update (bias correction)
+ *   scratch                              129 doubles; scratch[128] receives the unclipped gradient norm */
+int ringrnn_clip_adam(float* params, const float* grads, float* exp_avg, float* exp_avg_sq, size_t n, float lr,
+                      float beta1, float beta2, float eps, int step, float max_norm, double* scratch, void* stream);
+
 /* Launch accounting and per-kernel timing (the reference's counterpart is the NVTX / cudaProfiler
  * bracketing in legacy/bwd_fp32.py:705-740 and utils/benchmark.py:58-79).
  *   ringrnn_launch_count   kernels launched by this library since the last reset

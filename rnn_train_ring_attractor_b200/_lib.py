@@ -65,6 +65,8 @@ SYMBOLS = {
     "ringrnn_angle_loss_static": (C.c_int, [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                             C.c_float, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                             C.c_void_p, C.c_void_p]),
+    "ringrnn_clip_adam": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_float, C.c_float,
+                                    C.c_float, C.c_float, C.c_int, C.c_float, C.c_void_p, C.c_void_p]),
     "ringrnn_launch_count": (C.c_longlong, []),
     "ringrnn_timing_slots": (C.c_int, []),
     "ringrnn_timing_name": (C.c_char_p, [C.c_int]),
