@@ -337,7 +337,7 @@ def run_ours(args, wl):
     Wa, Wo = host["Wa"].to(dev), host["Wo"].to(dev)
     resident = tuple(pinned[k].to(dev) for k in ("A", "r_init", "target"))
     buf = torch.empty(dp.grad_buffer_numel(N, 2), dtype=torch.float32, device=dev)
-    step_fn = dp.fused_step_fn(Wa, host["J0"], host["J1"], Wo, 0.1, act, precision=prec)
+    step_fn = dp.fused_step_fn(Wa, host["J0"], host["J1"], Wo, 0.1, act, precision=prec, ckpt_every=args.ckpt_every)
 
     def step(inputs):
         return dp.train_step(step_fn, inputs, N, 2, B_global, T, buf=buf)
@@ -445,6 +445,8 @@ def run_ours(args, wl):
         "dtype": "bf16" if prec == "bf16" else "f32", "data": "synthetic",
         "config": {"workload": f"{args.workload}: N={N}, B={B_local} per GPU, T={T}, {act}, alpha=0.1, "
                                f"fused fwd+loss+bwd, precision mode {prec}"
+                               + (f", state checkpoints every {args.ckpt_every} steps + recompute in backward"
+                                  if args.ckpt_every else "")
                                + (f" (the configuration is defined on {wl['defined_on']} GPUs, global batch "
                                   f"{wl['B'] * wl['defined_on']}; this run has {world})"
                                   if wl.get("defined_on", world) != world and args.scaling == "weak" else ""),
@@ -473,6 +475,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--seq-len", type=int, default=0, help="override T (profiling on a smaller case of the same kernels)")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling)")
+    ap.add_argument("--ckpt-every", type=int, default=0,
+                    help="keep the state every K steps and recompute in backward (0 = keep every step)")
     args = ap.parse_args()
     if args.workload == "published":
         run_published_table(args)

@@ -50,7 +50,11 @@ enum { RINGRNN_WS_FWD = 0, RINGRNN_WS_SAVED = 1, RINGRNN_WS_BWD = 2 };
  *   A[B,T,a_dim], Wa[a_dim,N,N], Wo[N,N], r_init[B,N], all fp32, contiguous, device memory.
  * n_active / active_cols name the columns of A that are not identically zero (the root training
  * script pads the L/R signal to 16 columns with zeros, train_general_ring_no_gain.py:200-223);
- * n_active < 0 means "all a_dim columns".  Gradients of skipped columns are exactly zero. */
+ * n_active < 0 means "all a_dim columns".  Gradients of skipped columns are exactly zero.
+ * ckpt_every = K > 0 (bf16 mode, persistent kernels): the forward keeps only the fp32 state every K steps and the
+ * backward recomputes each stretch of K steps from its checkpoint before it propagates through it -- the saved
+ * storage shrinks from two bf16 tensors of T*B*N to T/K fp32 states of B*N, for one extra forward pass.  0 = keep every
+ * step (the default; faster whenever the saved tensors fit).  The fp32 mode and the stepwise path ignore it. */
 typedef struct RingRnnProblem {
   int B, T, N, a_dim;
   int activation; /* RINGRNN_ACT_*  */
@@ -62,6 +66,7 @@ typedef struct RingRnnProblem {
   const float* r_init;
   int n_active;
   int active_cols[RINGRNN_MAX_ACTIVE];
+  int ckpt_every;
 } RingRnnProblem;
 
 /* Forward.  Replaces fwd_cuda() (cpp/fwd.cu:21-50) and its launchers

@@ -25,7 +25,7 @@ class Problem(C.Structure):
                 ("activation", C.c_int), ("precision", C.c_int),
                 ("J0", C.c_float), ("J1", C.c_float), ("alpha", C.c_float),
                 ("A", C.c_void_p), ("Wa", C.c_void_p), ("Wo", C.c_void_p), ("r_init", C.c_void_p),
-                ("n_active", C.c_int), ("active_cols", C.c_int * MAX_ACTIVE)]
+                ("n_active", C.c_int), ("active_cols", C.c_int * MAX_ACTIVE), ("ckpt_every", C.c_int)]
 
 
 class FwdArgs(C.Structure):
@@ -111,8 +111,9 @@ def check(status):
         raise RingRnnError(status, text)
 
 
-def make_problem(B, T, N, a_dim, act, prec, J0, J1, alpha, A, Wa, Wo, r_init, active=None):
+def make_problem(B, T, N, a_dim, act, prec, J0, J1, alpha, A, Wa, Wo, r_init, active=None, ckpt_every=0):
     p = Problem()
+    p.ckpt_every = int(ckpt_every)
     p.B, p.T, p.N, p.a_dim = B, T, N, a_dim
     p.activation, p.precision = act, prec
     p.J0, p.J1, p.alpha = float(J0), float(J1), float(alpha)

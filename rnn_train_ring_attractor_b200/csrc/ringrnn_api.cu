@@ -59,6 +59,7 @@ int check_problem(const RingRnnProblem& p) {
   if (p.activation < RINGRNN_ACT_RELU || p.activation > RINGRNN_ACT_SILU) return RINGRNN_ERR_ARG;
   if (p.precision != RINGRNN_PREC_FP32 && p.precision != RINGRNN_PREC_BF16) return RINGRNN_ERR_ARG;
   if (p.n_active > p.a_dim || p.n_active > RINGRNN_MAX_ACTIVE) return RINGRNN_ERR_ARG;
+  if (p.ckpt_every < 0) return RINGRNN_ERR_ARG;
   if (p.n_active < 0 && p.a_dim > RINGRNN_MAX_ACTIVE) return RINGRNN_ERR_UNSUPPORTED;
   for (int k = 0; k < p.n_active; ++k)
     if (p.active_cols[k] < 0 || p.active_cols[k] >= p.a_dim) return RINGRNN_ERR_ARG;

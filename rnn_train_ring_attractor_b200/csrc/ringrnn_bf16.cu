@@ -145,9 +145,18 @@ size_t bf16_fwd_workspace_bytes(const RingRnnProblem& p) {
 size_t sign_mask_bytes(const RingRnnProblem& p, const Layout& l) {
   return align_up((size_t)p.T * (l.NP / 32) * 2 * l.BP * 4, 1024);
 }
-size_t bf16_saved_bytes(const RingRnnProblem& p) {
+// checkpoint interval in force (0 = every step is kept)
+int ckpt_interval(const RingRnnProblem& p) { return (p.ckpt_every > 0 && p.ckpt_every < p.T) ? p.ckpt_every : 0; }
+size_t ckpt_slot_bytes(const RingRnnProblem& p) { return (size_t)p.B * p.N * sizeof(float); }
+size_t saved_every_step_bytes(const RingRnnProblem& p) {
   const Layout l = layout_of(p);
   return (size_t)(2 * p.T + 1) * l.state_bytes + sign_mask_bytes(p, l);
+}
+// with checkpoints: [ceil(T/K)][B][N] fp32 states (slot 0 = r_init)
+size_t bf16_saved_bytes(const RingRnnProblem& p) {
+  const int K = ckpt_interval(p);
+  if (K == 0) return saved_every_step_bytes(p);
+  return align_up((size_t)((p.T + K - 1) / K) * ckpt_slot_bytes(p), 1024);
 }
 
 
@@ -164,11 +173,15 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   __nv_bfloat16* Wf = reinterpret_cast<__nv_bfloat16*>(w + 1024);
   __nv_bfloat16* R0 = reinterpret_cast<__nv_bfloat16*>(w + 1024 + l.w_bytes);
   float* dec_part = reinterpret_cast<float*>(w + 1024 + l.w_bytes + l.r0_bytes);
-  __nv_bfloat16* Rh = train ? static_cast<__nv_bfloat16*>(a.saved) : nullptr;
-  __nv_bfloat16* Dh = train ? Rh + (size_t)(p.T + 1) * l.BP * l.NP : nullptr;
-  uint32_t* Sg = train ? reinterpret_cast<uint32_t*>(static_cast<char*>(a.saved) + (size_t)(2 * p.T + 1) * l.state_bytes)
-                       : nullptr;
-  if (train) R0 = Rh;  // slot 0 of the saved state doubles as the initial A operand
+  const int K = train ? ckpt_interval(p) : 0;
+  const bool keep_all = train && K == 0;
+  __nv_bfloat16* Rh = keep_all ? static_cast<__nv_bfloat16*>(a.saved) : nullptr;
+  __nv_bfloat16* Dh = keep_all ? Rh + (size_t)(p.T + 1) * l.BP * l.NP : nullptr;
+  uint32_t* Sg = keep_all ? reinterpret_cast<uint32_t*>(static_cast<char*>(a.saved) + (size_t)(2 * p.T + 1) * l.state_bytes)
+                          : nullptr;
+  if (keep_all) R0 = Rh;  // slot 0 of the saved state doubles as the initial A operand
+  if (K > 0)              // checkpoint 0 is the initial state
+    RINGRNN_CUDA_TRY(cudaMemcpyAsync(a.saved, p.r_init, ckpt_slot_bytes(p), cudaMemcpyDeviceToDevice, s));
 
   if (a.status == nullptr) RINGRNN_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), s));
   ActiveCols ac;
@@ -189,7 +202,7 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   if (!make_tmap_bf16_2d(&tmW, Wf, (uint64_t)l.C * 2 * l.ng * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, 64))
     return RINGRNN_ERR_CUDA;
   // one map serves the initial-state loads (rows [0, BP)) and, in training, the saved-state stores (rows up to T*BP)
-  if (!make_tmap_bf16_2d(&tmR0, R0, (uint64_t)(train ? p.T + 1 : 1) * l.BP, (uint64_t)l.NP, 128, 64))
+  if (!make_tmap_bf16_2d(&tmR0, R0, (uint64_t)(keep_all ? p.T + 1 : 1) * l.BP, (uint64_t)l.NP, 128, 64))
     return RINGRNN_ERR_CUDA;
 
   const bool want_dec = a.dec_x || a.dec_y || a.dec_ta;
@@ -209,6 +222,9 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   fp.dec_u = a.dec_u; fp.dec_v = a.dec_v;
   fp.final_state = a.final_state;
   fp.status = status;
+  fp.t0 = 0; fp.T_total = p.T;
+  fp.ckpt = K > 0 ? static_cast<float*>(a.saved) : nullptr;
+  fp.ckpt_every = K;
   int rc = tc_forward_launch(p.activation, l.NP, l.pair, tmW, tmR0, fp, s);
   if (rc != RINGRNN_OK) return rc;
   if (want_dec) {
@@ -253,12 +269,13 @@ struct BwdLayout {
 
 // grad_A[b,t,cols[k]] = sum over slots of part[slot][k][t][b]   (`per_slot` entries k per slot, of which the first
 // cols.n are used)
+// (`part` covers the T steps that start at step t0 of a sequence of T_total)
 __global__ void da_reduce_kernel(const float* __restrict__ part, int slots, int per_slot, int B, int T, int BP, int a_dim,
-                                 ActiveCols cols, float* grad_A) {
+                                 ActiveCols cols, float* grad_A, int t0, int T_total) {
   const size_t total = (size_t)B * T;
   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const int t = (int)(idx / B), b = (int)(idx % B);
-    float* o = grad_A + ((size_t)b * T + t) * a_dim;
+    float* o = grad_A + ((size_t)b * T_total + t0 + t) * a_dim;
     for (int k = 0; k < cols.n; ++k) {
       float acc = 0.f;
       for (int sl = 0; sl < slots; ++sl) acc += part[(((size_t)sl * per_slot + k) * T + t) * BP + b];
@@ -288,9 +305,167 @@ BwdLayout bwd_layout_of(const RingRnnProblem& p, const Layout& l) {
 // BWD workspace: status(1024) | Wb | DL | split-K partials | dWcat | raw | dL/dA partials
 size_t bf16_bwd_workspace_bytes(const RingRnnProblem& p) {
   const Layout l = layout_of(p);
+  const int K = ckpt_interval(p);
+  if (K > 0) {
+    // with checkpoints: status | Wb | Wf | saved tensors of one stretch | DL, split-K partials, dW of one stretch |
+    //                   dWcat | raw | dL/dA partials of one stretch | two carry buffers
+    RingRnnProblem pc = p;
+    pc.T = K;
+    pc.ckpt_every = 0;
+    const BwdLayout b = bwd_layout_of(pc, l);
+    return 1024 + 2 * b.w_bytes + align_up(saved_every_step_bytes(pc), 1024) + b.dl_bytes + b.partial_bytes +
+           2 * b.dw_bytes + b.raw_bytes + b.da_bytes + 2 * align_up(ckpt_slot_bytes(p), 1024);
+  }
   const BwdLayout b = bwd_layout_of(p, l);
   return 1024 + b.w_bytes + b.dl_bytes + b.partial_bytes + b.dw_bytes + b.raw_bytes + b.da_bytes;
 }
+
+namespace {
+
+// out[e] = first ? in[e] : out[e] + in[e]
+__global__ void accumulate_kernel(float* __restrict__ out, const float* __restrict__ in, size_t n, int first) {
+  for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x)
+    out[e] = first ? in[e] : out[e] + in[e];
+}
+
+// Backward with checkpoints: the stretches of K steps are taken last to first; each is recomputed from its fp32
+// checkpoint by the forward kernel (which saves state, derivative history and sign masks of the stretch exactly as
+// the keep-everything forward would have), then the reverse-time kernel runs through it, starting from the gradient
+// the later stretch handed back, and the stretch's weight-gradient GEMM is added to the total.
+int bf16_backward_ckpt(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s, int K) {
+  const RingRnnProblem& p = a.p;
+  const Layout l = layout_of(p);
+  RingRnnProblem pc = p;
+  pc.T = K;
+  pc.ckpt_every = 0;
+  const BwdLayout bl = bwd_layout_of(pc, l);
+  char* w = static_cast<char*>(a.workspace);
+  int* status = a.status != nullptr ? a.status : reinterpret_cast<int*>(w);
+  w += 1024;
+  __nv_bfloat16* Wb = reinterpret_cast<__nv_bfloat16*>(w);
+  w += bl.w_bytes;
+  __nv_bfloat16* Wf = reinterpret_cast<__nv_bfloat16*>(w);
+  w += bl.w_bytes;
+  char* savedc = w;
+  w += align_up(saved_every_step_bytes(pc), 1024);
+  __nv_bfloat16* DL = reinterpret_cast<__nv_bfloat16*>(w);
+  w += bl.dl_bytes;
+  float* partial = reinterpret_cast<float*>(w);
+  w += bl.partial_bytes;
+  float* dWchunk = reinterpret_cast<float*>(w);
+  w += bl.dw_bytes;
+  float* dWcat = reinterpret_cast<float*>(w);
+  w += bl.dw_bytes;
+  float* raw = reinterpret_cast<float*>(w);
+  w += bl.raw_bytes;
+  float* dA_part = reinterpret_cast<float*>(w);
+  w += bl.da_bytes;
+  float* carry[2];
+  carry[0] = reinterpret_cast<float*>(w);
+  carry[1] = reinterpret_cast<float*>(w + align_up(ckpt_slot_bytes(p), 1024));
+  const float* ckpt = static_cast<const float*>(a.saved);
+
+  if (a.status == nullptr) RINGRNN_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), s));
+  ActiveCols ac;
+  ac.n = dp.n_mat - 1;
+  for (int k = 0; k < ac.n; ++k) ac.c[k] = dp.cols[k];
+  {
+    LaunchScope ls(K_PREP, s);
+    prep_weights_kernel<<<dim3(l.NP / 64, l.C * 2 * l.ng), 256, 0, s>>>(p.Wo, dp.Wa, ac, l.ng, p.N, l.NP, l.RB, Wf, Wb);
+  }
+  RINGRNN_CUDA_TRY(cudaGetLastError());
+  CUtensorMap tmWf, tmWb;
+  if (!make_tmap_bf16_2d(&tmWf, Wf, (uint64_t)l.C * 2 * l.ng * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, 64) ||
+      !make_tmap_bf16_2d(&tmWb, Wb, (uint64_t)l.C * 2 * l.ng * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, 64))
+    return RINGRNN_ERR_CUDA;
+  if (a.grad_A != nullptr)
+    RINGRNN_CUDA_TRY(cudaMemsetAsync(a.grad_A, 0, sizeof(float) * (size_t)p.B * p.T * p.a_dim, s));
+
+  const int n_ck = (p.T + K - 1) / K;
+  for (int c = n_ck - 1; c >= 0; --c) {
+    const int t0 = c * K, Tc = (p.T - t0 < K) ? p.T - t0 : K;
+    const float* state0 = ckpt + (size_t)c * p.B * p.N;
+    // saved tensors of the stretch, laid out as for a sequence of Tc steps
+    __nv_bfloat16* Rh = reinterpret_cast<__nv_bfloat16*>(savedc);
+    __nv_bfloat16* Dh = Rh + (size_t)(Tc + 1) * l.BP * l.NP;
+    uint32_t* Sg = reinterpret_cast<uint32_t*>(savedc + (size_t)(2 * Tc + 1) * l.state_bytes);
+    {
+      LaunchScope ls(K_PREP, s);
+      prep_r0_kernel<<<296, 256, 0, s>>>(state0, p.B, p.N, l.BP, l.NP, Rh);
+    }
+    RINGRNN_CUDA_TRY(cudaGetLastError());
+    CUtensorMap tmR0, tmDL;
+    if (!make_tmap_bf16_2d(&tmR0, Rh, (uint64_t)(Tc + 1) * l.BP, (uint64_t)l.NP, 128, 64) ||
+        !make_tmap_bf16_2d(&tmDL, DL, (uint64_t)Tc * l.BP, (uint64_t)bl.blocks * l.NP, 128, 64))
+      return RINGRNN_ERR_CUDA;
+
+    TcFwdParams fp;
+    memset(&fp, 0, sizeof(fp));
+    fp.B = p.B; fp.T = Tc; fp.N = p.N; fp.BP = l.BP; fp.a_dim = p.a_dim;
+    fp.colL = dp.n_mat > 1 ? dp.cols[0] : -1;
+    fp.colR = dp.n_mat > 2 ? dp.cols[1] : -1;
+    fp.ng = l.ng; fp.n_act = ac.n;
+    for (int k = 0; k < ac.n; ++k) fp.cols[k] = ac.c[k];
+    fp.n_tiles = l.BP / l.tile_rows;
+    fp.J0 = p.J0; fp.J1 = p.J1; fp.alpha = p.alpha;
+    fp.A = p.A; fp.r_init = state0;
+    fp.Rh = Rh; fp.Dh = Dh; fp.Sg = Sg;
+    fp.status = status;
+    fp.t0 = t0; fp.T_total = p.T;
+    int rc = tc_forward_launch(p.activation, l.NP, l.pair, tmWf, tmR0, fp, s);
+    if (rc != RINGRNN_OK) return rc;
+
+    TcBwdParams bp;
+    memset(&bp, 0, sizeof(bp));
+    bp.B = p.B; bp.T = Tc; bp.N = p.N; bp.BP = l.BP; bp.a_dim = p.a_dim;
+    bp.colL = fp.colL; bp.colR = fp.colR;
+    bp.ng = l.ng; bp.n_act = ac.n;
+    for (int k = 0; k < ac.n; ++k) bp.cols[k] = ac.c[k];
+    bp.n_tiles = fp.n_tiles;
+    bp.J0 = p.J0; bp.J1 = p.J1; bp.alpha = p.alpha;
+    bp.A = p.A; bp.Dh = Dh; bp.Sg = Sg;
+    bp.grad_output = a.grad_output;
+    bp.coef_x = a.coef_x; bp.coef_y = a.coef_y; bp.coef_s = a.coef_s;
+    bp.dec_u = a.dec_u; bp.dec_v = a.dec_v;
+    bp.DL = DL;
+    bp.grad_r_init = (c == 0) ? a.grad_r_init : carry[c & 1];
+    bp.Rh = Rh;
+    bp.dA_part = a.grad_A != nullptr ? dA_part : nullptr;
+    bp.status = status;
+    bp.t0 = t0; bp.T_total = p.T;
+    bp.carry_in = (c == n_ck - 1) ? nullptr : carry[(c + 1) & 1];
+    rc = tc_backward_launch(l.NP, l.pair, tmWb, tmDL, bp, s);
+    if (rc != RINGRNN_OK) return rc;
+
+    if (a.grad_A != nullptr) {
+      LaunchScope ls(K_REDUCE, s);
+      da_reduce_kernel<<<296, 256, 0, s>>>(dA_part, bl.da_slots, bl.da_per_slot, p.B, Tc, l.BP, p.a_dim, ac, a.grad_A, t0,
+                                           p.T);
+      RINGRNN_CUDA_TRY(cudaGetLastError());
+    }
+    rc = tc_gemm(1, DL, Rh, partial, dWchunk, bl.blocks * l.NP, l.NP, (long long)Tc * l.BP, gemm_splits(l, Tc), status, s);
+    if (rc != RINGRNN_OK) return rc;
+    {
+      LaunchScope ls(K_REDUCE, s);
+      accumulate_kernel<<<296, 256, 0, s>>>(dWcat, dWchunk, (size_t)bl.blocks * l.NP * l.NP, c == n_ck - 1 ? 1 : 0);
+    }
+    RINGRNN_CUDA_TRY(cudaGetLastError());
+  }
+  const size_t NN = (size_t)p.N * p.N;
+  RINGRNN_CUDA_TRY(cudaMemsetAsync(a.grad_Wa, 0, sizeof(float) * (size_t)p.a_dim * NN, s));
+  {
+    LaunchScope ls(K_REDUCE, s);
+    unpack_dw_kernel<<<296, 256, 0, s>>>(dWcat, p.N, l.NP, p.J1, ac, a.grad_Wo, a.grad_Wa, raw);
+  }
+  RINGRNN_CUDA_TRY(cudaGetLastError());
+  if (a.grad_J != nullptr) {
+    int rc = launch_grad_j(raw, p.Wo, NN, a.grad_J, reinterpret_cast<double*>(partial), s);
+    if (rc != RINGRNN_OK) return rc;
+  }
+  return RINGRNN_OK;
+}
+
+}  // namespace
 
 
 int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s) {
@@ -301,6 +476,7 @@ int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   if ((reinterpret_cast<uintptr_t>(a.workspace) & 255) != 0) return RINGRNN_ERR_WORKSPACE;
   if (a.saved == nullptr || a.saved_bytes < bf16_saved_bytes(p) || (reinterpret_cast<uintptr_t>(a.saved) & 255) != 0)
     return RINGRNN_ERR_WORKSPACE;
+  if (ckpt_interval(p) > 0) return bf16_backward_ckpt(a, dp, s, ckpt_interval(p));
   char* w = static_cast<char*>(a.workspace);
   int* status = a.status != nullptr ? a.status : reinterpret_cast<int*>(w);
   w += 1024;
@@ -350,6 +526,7 @@ int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   bp.Rh = Rh;
   bp.dA_part = a.grad_A != nullptr ? dA_part : nullptr;
   bp.status = status;
+  bp.t0 = 0; bp.T_total = p.T;
   CUtensorMap tmDL;
   if (!make_tmap_bf16_2d(&tmDL, DL, (uint64_t)p.T * l.BP, (uint64_t)bl.blocks * l.NP, 128, 64)) return RINGRNN_ERR_CUDA;
   int rc = tc_backward_launch(l.NP, l.pair, tmW, tmDL, bp, s);
@@ -358,7 +535,8 @@ int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   if (a.grad_A != nullptr) {
     RINGRNN_CUDA_TRY(cudaMemsetAsync(a.grad_A, 0, sizeof(float) * (size_t)p.B * p.T * p.a_dim, s));
     LaunchScope ls(K_REDUCE, s);
-    da_reduce_kernel<<<296, 256, 0, s>>>(dA_part, bl.da_slots, bl.da_per_slot, p.B, p.T, l.BP, p.a_dim, ac, a.grad_A);
+    da_reduce_kernel<<<296, 256, 0, s>>>(dA_part, bl.da_slots, bl.da_per_slot, p.B, p.T, l.BP, p.a_dim, ac, a.grad_A, 0,
+                                         p.T);
     RINGRNN_CUDA_TRY(cudaGetLastError());
   }
   // dWcat[blocks*NP, NP] = DL^T [blocks*NP, T*BP] x Rh[0..T) [T*BP, NP]

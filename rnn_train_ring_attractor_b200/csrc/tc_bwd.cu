@@ -70,7 +70,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       const bool valid = b < p.B;
       float master[64];  // carry on entry of `produce`, g_t afterwards
 #pragma unroll
-      for (int j = 0; j < 64; ++j) master[j] = 0.f;
+      for (int s = 0; s < 2; ++s)
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int n = nq + 64 * s + j;
+          master[s * 32 + j] = (p.carry_in != nullptr && valid && n < p.N) ? __ldg(p.carry_in + (size_t)b * p.N + n) : 0.f;
+        }
       float L = 0.f, R = 0.f;        // action scalars of the step whose delta is in flight
       float Ln = 0.f, Rn = 0.f, cx = 0.f, cy = 0.f, cs = 0.f;  // prefetched for the next `produce`
       uint4 dv[8];                   // prefetched F'(re_t) (bf16): [s*4 + v]
@@ -80,13 +85,14 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       auto prefetch = [&](int t) {
         Ln = 0.f; Rn = 0.f; cx = 0.f; cy = 0.f; cs = 0.f;
         if (valid) {
-          const float* at = p.A + ((size_t)b * T + t) * p.a_dim;
+          const size_t bt = (size_t)b * p.T_total + p.t0 + t;
+          const float* at = p.A + bt * p.a_dim;
           if (!GEN && p.colL >= 0) Ln = __ldg(at + p.colL);
           if (!GEN && p.colR >= 0) Rn = __ldg(at + p.colR);
           if (has_coef) {
-            cx = __ldg(p.coef_x + (size_t)b * T + t);
-            cy = __ldg(p.coef_y + (size_t)b * T + t);
-            cs = __ldg(p.coef_s + (size_t)b * T + t);
+            cx = __ldg(p.coef_x + bt);
+            cy = __ldg(p.coef_y + bt);
+            cs = __ldg(p.coef_s + bt);
           }
         }
 #pragma unroll
@@ -110,7 +116,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (p.grad_output != nullptr && valid) {
 #pragma unroll
           for (int s = 0; s < 2; ++s) {
-            const float* gsrc = p.grad_output + ((size_t)t * p.B + b) * p.N + nq + 64 * s;
+            const float* gsrc = p.grad_output + ((size_t)(p.t0 + t) * p.B + b) * p.N + nq + 64 * s;
             if ((p.N & 3) == 0) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4)
@@ -184,7 +190,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           }
         } else {
           // one scaled copy per active column: block 1 + k = A[b,t,cols[k]] * delta_t
-          const float* at = p.A + ((size_t)b * T + t) * p.a_dim;
+          const float* at = p.A + ((size_t)b * p.T_total + p.t0 + t) * p.a_dim;
           for (int k = 0; k < p.n_act; ++k) {
             const float ak = valid ? __ldg(at + p.cols[k]) : 0.f;
 #pragma unroll
@@ -214,7 +220,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         for (int s = 0; s < 2; ++s) {
           if constexpr (GEN) {
             // carry of sub-slice s gathered over the weight groups; one accumulator per (s, group)
-            const float* at = p.A + ((size_t)b * T + t) * p.a_dim;
+            const float* at = p.A + ((size_t)b * p.T_total + p.t0 + t) * p.a_dim;
             for (int grp = 0; grp < ng; ++grp) {
               const int i0 = 3 * grp - 1;  // index into cols[] of the group's first matrix (-1: Wo)
               float k0, k1 = 0.f, k2 = 0.f;

@@ -86,7 +86,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           master[s * 32 + j] = (valid && n < p.N) ? __ldg(p.r_init + (size_t)b * p.N + n) : 0.f;
         }
       for (int t = 0; t < T; ++t, ++g) {
-        const float* at = p.A + ((size_t)b * T + t) * p.a_dim;  // this sample's action scalars (read only if valid)
+        // this sample's action scalars (read only if valid)
+        const float* at = p.A + ((size_t)b * p.T_total + p.t0 + t) * p.a_dim;
         float L = 0.f, R = 0.f;
         if (!GEN && valid) {
           if (p.colL >= 0) L = __ldg(at + p.colL);
@@ -226,7 +227,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           freed.end_of_step(c, g, 208);
         }
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 11);
-        // off the critical path: fp32 history, decode sums
+        // off the critical path: checkpoint of the fp32 state, fp32 history, decode sums
+        if (p.ckpt != nullptr && valid && t + 1 < T && (t + 1) % p.ckpt_every == 0) {
+          float* dst = p.ckpt + ((size_t)((t + 1) / p.ckpt_every) * p.B + b) * p.N + nq;
+#pragma unroll
+          for (int s = 0; s < 2; ++s)
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nq + 64 * s + j < p.N) dst[64 * s + j] = master[s * 32 + j];
+        }
         if (p.hist != nullptr && valid) {
 #pragma unroll
           for (int s = 0; s < 2; ++s) {

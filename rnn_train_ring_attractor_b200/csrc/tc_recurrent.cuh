@@ -77,6 +77,11 @@ struct TcFwdParams {
   // group 0 = {Wo, Wa[cols[0]], Wa[cols[1]]} + ones row, group m = {Wa[cols[3m-1]], Wa[cols[3m]], Wa[cols[3m+1]]}
   int ng, n_act;
   int cols[RINGRNN_MAX_ACTIVE];
+  // A launch may cover steps [t0, t0 + T) of a longer sequence of T_total steps (recompute of one stretch between
+  // checkpoints): A is indexed with the global step; everything this launch writes with the local one.
+  int t0, T_total;
+  float* ckpt;           // [ceil(T/ckpt_every)][B][N] fp32: slot c receives the state after step c*ckpt_every - 1
+  int ckpt_every;        //   (slot 0, the initial state, is the caller's); nullptr = none
 };
 
 struct TcBwdParams {
@@ -99,6 +104,10 @@ struct TcBwdParams {
   int* status;
   int ng, n_act;                // as in TcFwdParams; DL then has 1 + n_act column blocks [delta | A_k * delta ...]
   int cols[RINGRNN_MAX_ACTIVE];
+  // steps [t0, t0 + T) of a sequence of T_total: A, grad_output and the loss coefficients are indexed with the global
+  // step, the saved tensors, DL and the dL/dA partial sums with the local one
+  int t0, T_total;
+  const float* carry_in;        // [B,N] gradient flowing into the last state of this stretch from later steps, or nullptr
 };
 
 // `generic`: more than two active action columns (p.ng > 1 weight groups); NP <= 512, no CTA pairs

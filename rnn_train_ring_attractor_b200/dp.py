@@ -56,8 +56,8 @@ def train_step(step_fn, local_inputs, N, a_dim, global_batch, T, buf=None, group
     return loss, out
 
 
-def fused_step_fn(Wa, J0, J1, Wo, alpha, activation, bump_weight=0.2, precision=None):
-    """step_fn for :func:`train_step` backed by the fused CUDA operator."""
+def fused_step_fn(Wa, J0, J1, Wo, alpha, activation, bump_weight=0.2, precision=None, ckpt_every=0):
+    """step_fn for :func:`train_step` backed by the fused CUDA operator (`ckpt_every`: see ring_rnn_fused)."""
     from .fused import ring_rnn_fused
 
     def fn(local_inputs, inv_count, buf):
@@ -65,7 +65,7 @@ def fused_step_fn(Wa, J0, J1, Wo, alpha, activation, bump_weight=0.2, precision=
         Wa_ = Wa.detach().requires_grad_(True)
         Wo_ = Wo.detach().requires_grad_(True)
         loss, parts, _, _ = ring_rnn_fused(A, Wa_, J0, J1, Wo_, r_init, alpha, activation, target, bump_weight,
-                                           inv_count, precision, buf)
+                                           inv_count, precision, buf, ckpt_every)
         loss.backward()
         return parts
 

@@ -35,11 +35,11 @@ def decode_vectors(N, device):
 
 class RingRnnFusedFunc(Function):
     """apply(action_signal, Wa, J0, J1, Wo, r_init, alpha, activation, target_angle, bump_weight, inv_count,
-    precision, grad_buffer) -> (loss, loss_parts[2], decoded[B,T], final_state[B,N])"""
+    precision, grad_buffer, ckpt_every) -> (loss, loss_parts[2], decoded[B,T], final_state[B,N])"""
 
     @staticmethod
     def forward(ctx, action_signal, Wa, J0, J1, Wo, r_init, alpha, activation_name, target, bump_weight,
-                inv_count, precision, grad_buffer):
+                inv_count, precision, grad_buffer, ckpt_every=0):
         B, T, a_dim = action_signal.shape
         N = Wa.shape[1]
         if activation_name not in _lib.ACT:
@@ -60,7 +60,8 @@ class RingRnnFusedFunc(Function):
         with torch.cuda.device(dev):
             stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
             p = _lib.make_problem(B, T, N, a_dim, act, prec, _scalar(J0), _scalar(J1), alpha,
-                                  action_signal.data_ptr(), Wa.data_ptr(), Wo.data_ptr(), r_init.data_ptr(), active)
+                                  action_signal.data_ptr(), Wa.data_ptr(), Wo.data_ptr(), r_init.data_ptr(), active,
+                                  ckpt_every=ckpt_every)
             scal = torch.empty(6, B, T, device=dev, dtype=torch.float32)  # x, y, ta, coef_x, coef_y, coef_s
             decoded = torch.empty(B, T, device=dev, dtype=torch.float32)
             final_state = torch.empty(B, N, device=dev, dtype=torch.float32)
@@ -86,6 +87,7 @@ class RingRnnFusedFunc(Function):
         ctx.save_for_backward(action_signal, Wa, Wo, r_init, saved, scal, u, v)
         ctx.J0, ctx.J1, ctx.alpha, ctx.act, ctx.active, ctx.prec = J0, J1, alpha, act, active, prec
         ctx.grad_buffer = grad_buffer
+        ctx.ckpt_every = ckpt_every
         ctx.mark_non_differentiable(parts, decoded, final_state)
         return loss, parts, decoded, final_state
 
@@ -102,7 +104,7 @@ class RingRnnFusedFunc(Function):
         with torch.cuda.device(dev):
             p = _lib.make_problem(B, T, N, a_dim, ctx.act, ctx.prec, _scalar(ctx.J0), _scalar(ctx.J1), ctx.alpha,
                                   action_signal.data_ptr(), Wa.data_ptr(), Wo.data_ptr(), r_init.data_ptr(),
-                                  ctx.active)
+                                  ctx.active, ckpt_every=ctx.ckpt_every)
             if ctx.grad_buffer is not None:
                 # one contiguous buffer [Wo | Wa | dJ0 dJ1] so a data-parallel step all-reduces it in one call
                 buf = ctx.grad_buffer
@@ -142,20 +144,22 @@ class RingRnnFusedFunc(Function):
                 grad_a.mul_(g_loss)
         gJ0 = grad_J[0].reshape(ctx.J0.shape) if (torch.is_tensor(ctx.J0) and ctx.J0.requires_grad) else None
         gJ1 = grad_J[1].reshape(ctx.J1.shape) if (torch.is_tensor(ctx.J1) and ctx.J1.requires_grad) else None
-        return (grad_a, grad_Wa, gJ0, gJ1, grad_Wo, grad_r, None, None, None, None, None, None, None)
+        return (grad_a, grad_Wa, gJ0, gJ1, grad_Wo, grad_r, None, None, None, None, None, None, None, None)
 
 
 def ring_rnn_fused(action_signal, Wa, J0, J1, Wo, r_init, alpha, activation, target_angle, bump_weight=0.2,
-                   inv_count=None, precision=None, grad_buffer=None):
+                   inv_count=None, precision=None, grad_buffer=None, ckpt_every=0):
     """One fused training forward: returns (loss, loss_parts, decoded_angle[B,T], final_state[B,N]).
 
     loss = mean(2 - 2cos(decoded - target)) + bump_weight * mean((ta_t - ta_0)^2), the total of
     train_general_ring_no_gain.py:327-330.  `inv_count` (default 1/(B*T)) lets a data-parallel caller
     normalise by the global batch.  `grad_buffer`: optional flat fp32 tensor of (1+a)*N*N+2 elements that
-    receives [dWo | dWa | dJ0 dJ1] contiguously during backward.
+    receives [dWo | dWa | dJ0 dJ1] contiguously during backward.  `ckpt_every` = K > 0 keeps only the fp32 state
+    every K steps (the "state checkpoints every 64 steps and recompute in backward" of the long-sequence
+    configuration): T/K states of B*N floats instead of two bf16 tensors of T*B*N, for one extra forward pass.
     """
     return RingRnnFusedFunc.apply(action_signal, Wa, J0, J1, Wo, r_init, alpha, activation, target_angle,
-                                  bump_weight, inv_count, precision, grad_buffer)
+                                  bump_weight, inv_count, precision, grad_buffer, ckpt_every)
 
 
 def ring_rnn_rollout(action_signal, Wa, J0, J1, Wo, r_init, alpha, activation, precision=None):

@@ -397,3 +397,37 @@ def test_linearity_in_batch_at_scale(prec):
         acc_a += b["dWa"]
     # identical per-sample arithmetic; only the order of the fp32 sums over the batch differs
     assert orc.rel_err(acc_o, full["dWo"]) < 1e-5 and orc.rel_err(acc_a, full["dWa"]) < 1e-5
+
+
+@pytest.mark.parametrize("cfg", [(256, 300, 50, "tanh", 16), (120, 128, 120, "tanh", 64), (512, 192, 12, "gelu", 5),
+                                 (1024, 130, 9, "tanh", 4), (96, 20000, 7, "silu", 3)],
+                         ids=lambda c: "N%d-B%d-T%d-%s-K%d" % c)
+def test_checkpoint_and_recompute_matches_keeping_every_step(cfg):
+    """ckpt_every = K: the forward keeps only the fp32 state every K steps, the backward recomputes each stretch from
+    its checkpoint.  The recompute starts from the exact fp32 state, so everything per step is bit-identical to the
+    keep-everything run; the weight gradients are summed stretch by stretch (another fp32 order)."""
+    from rnn_train_ring_attractor_b200.fused import ring_rnn_fused
+    N, B, T, act, K = cfg
+    case = orc.make_case(N, B, T, act, seed=3)
+    A, r0, target = _dev(case.A, case.r_init, case.target)
+    out = {}
+    for ck in (0, K):
+        Wa = case.Wa.cuda().requires_grad_(True)
+        Wo = case.Wo.cuda().requires_grad_(True)
+        J0 = torch.tensor(case.J0, device="cuda", requires_grad=True)
+        J1 = torch.tensor(case.J1, device="cuda", requires_grad=True)
+        r0g = r0.clone().requires_grad_(True)
+        Ag = A.clone().requires_grad_(True)
+        loss, parts, decoded, final = ring_rnn_fused(Ag, Wa, J0, J1, Wo, r0g, case.alpha, act, target, precision="bf16",
+                                                     ckpt_every=ck)
+        loss.backward()
+        out[ck] = dict(loss=loss.detach(), decoded=decoded, final=final, dWa=Wa.grad, dWo=Wo.grad, dJ0=J0.grad,
+                       dJ1=J1.grad, dr0=r0g.grad, dA=Ag.grad)
+    a, b = out[0], out[K]
+    assert torch.equal(a["loss"], b["loss"]) and torch.equal(a["decoded"], b["decoded"]) and torch.equal(a["final"], b["final"])
+    assert torch.equal(a["dr0"], b["dr0"]), "the reverse pass through recomputed stretches must reproduce delta bit for bit"
+    assert torch.equal(a["dA"], b["dA"])
+    for k in ("dWo", "dWa"):
+        assert orc.rel_err(b[k], a[k]) < 1e-5, k
+    assert abs(float(a["dJ0"]) - float(b["dJ0"])) < 1e-4 * max(1.0, float(a["dWo"].norm()) * N / abs(case.J1))
+    assert abs(float(a["dJ1"]) - float(b["dJ1"])) < 1e-4 * max(1.0, float(a["dWo"].norm()) * float(case.Wo.norm()) / abs(case.J1))
