@@ -44,7 +44,7 @@ def _problem(**kw):
     d = dict(B=8, T=5, N=24, a_dim=2, act=2, prec=0, J0=-0.1, J1=0.1, alpha=0.1, A=1, Wa=1, Wo=1, r_init=1)
     d.update(kw)
     return _lib.make_problem(d["B"], d["T"], d["N"], d["a_dim"], d["act"], d["prec"], d["J0"], d["J1"], d["alpha"],
-                             d["A"], d["Wa"], d["Wo"], d["r_init"], d.get("active"))
+                             d["A"], d["Wa"], d["Wo"], d["r_init"], d.get("active"), d.get("ckpt_every", 0))
 
 
 def test_argument_validation_returns_status_not_exit(L):
@@ -90,6 +90,39 @@ def test_workspace_sizes(L):
     pa = _problem(a_dim=16, active=[0, 1])
     pf = _problem(a_dim=16)
     assert L.ringrnn_workspace_bytes(C.byref(pa), _lib.WS_FWD, 1) < L.ringrnn_workspace_bytes(C.byref(pf), _lib.WS_FWD, 1)
+
+
+def test_bf16_mode_sizes_every_shape_and_checkpoints_shrink_the_saved_state(L):
+    """bf16 mode takes any shape with up to 64 active action columns (persistent kernels or one GEMM per timestep);
+    checkpoints replace the per-step saved tensors by T/K states."""
+    unsupported = C.c_size_t(-1).value
+    for N, a_dim, B in ((120, 2, 128), (512, 2, 4096), (1024, 2, 1024), (512, 16, 4096), (512, 16, 256),
+                        (1024, 16, 256), (2048, 64, 256), (1100, 3, 40)):
+        p = _problem(B=B, T=20, N=N, a_dim=a_dim, prec=1)
+        sizes = [L.ringrnn_workspace_bytes(C.byref(p), w, 0) for w in (_lib.WS_FWD, _lib.WS_SAVED, _lib.WS_BWD)]
+        assert all(0 < x != unsupported for x in sizes), (N, a_dim, B, sizes)
+    too_wide = _problem(B=8, T=4, N=64, a_dim=80, prec=1)   # more than RINGRNN_MAX_ACTIVE columns
+    assert L.ringrnn_workspace_bytes(C.byref(too_wide), _lib.WS_FWD, 0) == unsupported
+    keep = _problem(B=1024, T=2000, N=1024, prec=1)
+    ckpt = _problem(B=1024, T=2000, N=1024, prec=1, ckpt_every=64)
+    s_keep = L.ringrnn_workspace_bytes(C.byref(keep), _lib.WS_SAVED, 0)
+    s_ckpt = L.ringrnn_workspace_bytes(C.byref(ckpt), _lib.WS_SAVED, 0)
+    assert s_keep >= 2 * 2000 * 1024 * 1024 * 2              # two bf16 tensors of T*B*N
+    assert 32 * 1024 * 1024 * 4 <= s_ckpt < s_keep // 50     # ceil(2000/64) = 32 fp32 states of B*N
+    w_keep = L.ringrnn_workspace_bytes(C.byref(keep), _lib.WS_BWD, 0)
+    w_ckpt = L.ringrnn_workspace_bytes(C.byref(ckpt), _lib.WS_BWD, 0)
+    assert w_ckpt < w_keep // 10                             # one stretch of 64 steps instead of all 2000
+    bad = _problem(prec=1, ckpt_every=-1)
+    assert L.ringrnn_workspace_bytes(C.byref(bad), _lib.WS_FWD, 0) == unsupported
+    same = _problem(B=64, T=16, N=128, prec=1, ckpt_every=16)  # K >= T: nothing to checkpoint
+    base = _problem(B=64, T=16, N=128, prec=1)
+    assert L.ringrnn_workspace_bytes(C.byref(same), _lib.WS_SAVED, 0) == L.ringrnn_workspace_bytes(C.byref(base), _lib.WS_SAVED, 0)
+
+
+def test_clip_adam_validates_arguments(L):
+    assert L.ringrnn_clip_adam(None, 1, 1, 1, 10, 1e-3, 0.9, 0.999, 1e-8, 1, 1.0, 1, None) == 1
+    assert L.ringrnn_clip_adam(1, 1, 1, 1, 10, 1e-3, 0.9, 0.999, 1e-8, 0, 1.0, 1, None) == 1   # steps count from 1
+    assert L.ringrnn_clip_adam(1, 1, 1, 1, 0, 1e-3, 0.9, 0.999, 1e-8, 1, 1.0, 1, None) == 0    # nothing to do
 
 
 def test_python_surface_mirrors_reference_names():
