@@ -400,7 +400,7 @@ def test_linearity_in_batch_at_scale(prec):
 
 
 @pytest.mark.parametrize("cfg", [(256, 300, 50, "tanh", 16), (120, 128, 120, "tanh", 64), (512, 192, 12, "gelu", 5),
-                                 (1024, 130, 9, "tanh", 4), (96, 20000, 7, "silu", 3)],
+                                 (1024, 130, 9, "tanh", 4), (96, 20000, 7, "silu", 3), (192, 1100, 10, "tanh", 4)],
                          ids=lambda c: "N%d-B%d-T%d-%s-K%d" % c)
 def test_checkpoint_and_recompute_matches_keeping_every_step(cfg):
     """ckpt_every = K: the forward keeps only the fp32 state every K steps, the backward recomputes each stretch from
@@ -409,6 +409,11 @@ def test_checkpoint_and_recompute_matches_keeping_every_step(cfg):
     from rnn_train_ring_attractor_b200.fused import ring_rnn_fused
     N, B, T, act, K = cfg
     case = orc.make_case(N, B, T, act, seed=3)
+    if N == 192:
+        # five active action columns on the persistent kernels (weight groups): the same run with a wider signal
+        g = torch.Generator().manual_seed(11)
+        case.A = torch.rand(B, T, 5, generator=g) * 0.5
+        case.Wa = torch.randn(5, N, N, generator=g) * 0.01
     A, r0, target = _dev(case.A, case.r_init, case.target)
     out = {}
     for ck in (0, K):
