@@ -70,6 +70,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     const int slot = 2 * q + h;
     const float J0 = p.J0, J1 = p.J1, alpha = p.alpha, beta = 1.f - p.alpha;
     const bool want_dec = p.dec_part != nullptr;
+    const bool padded = p.N != NP;  // some of the NP columns are padding
     const int rq = (2 * q) / C_::SLOTS;  // the K round this CTA's own chunks belong to
     FreePhases<NP, PAIR> freed;
     uint32_t g = 0;
@@ -184,11 +185,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               }
             }
             act_group<ACT, 8>(re, f, d);
+            if (padded) {  // neurons beyond N stay at zero (their master state is zero): one uniform branch per group
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                if (nq + 64 * s + j0 + e >= p.N) { f[e] = 0.f; d[e] = 0.f; }
+            }
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
               const int idx = s * 32 + j0 + e;
-              float r = fmaf(alpha, f[e], beta * master[idx]);
-              if (nq + 64 * s + j0 + e >= p.N) { r = 0.f; d[e] = 0.f; }
+              const float r = fmaf(alpha, f[e], beta * master[idx]);
               master[idx] = r;
               f[e] = r;
               pos |= (r > 0.f ? 1u : 0u) << (j0 + e);
