@@ -139,6 +139,15 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             const uint32_t dw[4] = {dv[s * 4 + v].x, dv[s * 4 + v].y, dv[s * 4 + v].z, dv[s * 4 + v].w};
+            // the eight decode weights of this group in four 16-byte shared-memory loads (same address in every lane)
+            float uu[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, vv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (has_coef) {
+              const float4* up = reinterpret_cast<const float4*>(uv + 64 * s + 32 * h + 8 * v);
+              const float4* vp = reinterpret_cast<const float4*>(uv + 128 + 64 * s + 32 * h + 8 * v);
+              const float4 u0 = up[0], u1 = up[1], v0 = vp[0], v1 = vp[1];
+              uu[0] = u0.x; uu[1] = u0.y; uu[2] = u0.z; uu[3] = u0.w; uu[4] = u1.x; uu[5] = u1.y; uu[6] = u1.z; uu[7] = u1.w;
+              vv[0] = v0.x; vv[1] = v0.y; vv[2] = v0.z; vv[3] = v0.w; vv[4] = v1.x; vv[5] = v1.y; vv[6] = v1.z; vv[7] = v1.w;
+            }
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
               float dl[2];
@@ -149,8 +158,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 float gg = master[idx];
                 if (has_coef) {
                   const float sg = (float)((mpos[s] >> j) & 1u) - (float)((mneg[s] >> j) & 1u);
-                  gg = fmaf(cx, uv[64 * s + 32 * h + j], gg);
-                  gg = fmaf(cy, uv[128 + 64 * s + 32 * h + j], gg);
+                  gg = fmaf(cx, uu[w * 2 + e], gg);
+                  gg = fmaf(cy, vv[w * 2 + e], gg);
                   gg = fmaf(cs, sg, gg);
                 }
                 master[idx] = gg;

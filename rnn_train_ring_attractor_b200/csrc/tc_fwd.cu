@@ -198,10 +198,19 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               f[e] = r;
               pos |= (r > 0.f ? 1u : 0u) << (j0 + e);
               neg |= (r < 0.f ? 1u : 0u) << (j0 + e);
-              if (want_dec) {
-                px = fmaf(r, uv[64 * s + 32 * h + j0 + e], px);
-                py = fmaf(r, uv[128 + 64 * s + 32 * h + j0 + e], py);
-                pa += fabsf(r);
+            }
+            if (want_dec) {
+              // the group's eight decode weights in four 16-byte shared-memory loads (same address in every lane)
+              const float4* up = reinterpret_cast<const float4*>(uv + 64 * s + 32 * h + j0);
+              const float4* vp = reinterpret_cast<const float4*>(uv + 128 + 64 * s + 32 * h + j0);
+              const float4 u0 = up[0], u1 = up[1], v0 = vp[0], v1 = vp[1];
+              const float uu[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+              const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                px = fmaf(f[e], uu[e], px);
+                py = fmaf(f[e], vv[e], py);
+                pa += fabsf(f[e]);
               }
             }
 #pragma unroll
