@@ -80,7 +80,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       float L = 0.f, R = 0.f;        // action scalars of the step whose delta is in flight
       float Ln = 0.f, Rn = 0.f, cx = 0.f, cy = 0.f, cs = 0.f;  // prefetched for the next `produce`
       uint4 dv[8];                   // prefetched F'(re_t) (bf16): [s*4 + v]
-      uint32_t mpos[2], mneg[2];     // prefetched sign masks of r_t per sub-slice
+      uint32_t mzero[2], mneg[2];    // prefetched masks of r_t per sub-slice: exact zeros, sign bits
 
       // loads for produce(t); issued before the wait on the accumulators so that their latency is hidden
       auto prefetch = [&](int t) {
@@ -100,11 +100,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         for (int s = 0; s < 2; ++s) {
           const int n32 = (nq + 64 * s) >> 5;
           load_blocked(p.Dh + blocked_offset(t, b, n32, p.BP, NP), lane, dv + 4 * s);
-          mpos[s] = 0u;
+          mzero[s] = 0u;
           mneg[s] = 0u;
           if (has_coef) {
             const uint32_t* sg = p.Sg + (((size_t)t * (NP >> 5) + n32) * 2) * p.BP + b;
-            mpos[s] = __ldg(sg);
+            mzero[s] = __ldg(sg);
             mneg[s] = __ldg(sg + p.BP);
           }
         }
@@ -136,6 +136,14 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         uint32_t packed[32];
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
+          // d|r|/dr = sign(r_t) is applied below as +cs or -cs by the sign bit alone (two instructions per element);
+          // where r_t is an exact zero (rare; always so for padding columns) the term must vanish: take it out of
+          // the carry beforehand
+          if (has_coef && mzero[s] != 0u) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (mzero[s] & (1u << j)) master[s * 32 + j] -= (mneg[s] & (1u << j)) ? -cs : cs;
+          }
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             const uint32_t dw[4] = {dv[s * 4 + v].x, dv[s * 4 + v].y, dv[s * 4 + v].z, dv[s * 4 + v].w};
@@ -157,10 +165,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 const int idx = s * 32 + j;
                 float gg = master[idx];
                 if (has_coef) {
-                  const float sg = (float)((mpos[s] >> j) & 1u) - (float)((mneg[s] >> j) & 1u);
                   gg = fmaf(cx, uu[w * 2 + e], gg);
                   gg = fmaf(cy, vv[w * 2 + e], gg);
-                  gg = fmaf(cs, sg, gg);
+                  gg += (mneg[s] & (1u << j)) ? -cs : cs;  // + cs * sign(r_t); exact zeros were pre-compensated
                 }
                 master[idx] = gg;
                 const float dact = e ? bf16_hi(dw[w]) : bf16_lo(dw[w]);

@@ -66,7 +66,7 @@ struct TcFwdParams {
   const float* r_init;   // [B,N]
   __nv_bfloat16* Rh;     // [T+1][BP][NP] (slot 0 = bf16(r_init), prepared before launch) or nullptr
   __nv_bfloat16* Dh;     // F'(re_t), blocked layout (tc_recurrent.cuh), T*BP*NP elements, or nullptr
-  uint32_t* Sg;          // [T][NP/32][2][BP] bit masks of r_t > 0 and r_t < 0 (bit j = neuron 32*block + j), or nullptr
+  uint32_t* Sg;          // [T][NP/32][2][BP] bit masks "r_t == 0" and "sign bit of r_t" (bit j = neuron 32*block + j), or nullptr
   float* hist;           // [T,B,N] or nullptr
   float* dec_part;       // [2C][3][T][BP] or nullptr
   const float* dec_u;    // [N]
@@ -89,7 +89,7 @@ struct TcBwdParams {
   float J0, J1, alpha;
   const float* A;               // [B,T,a_dim]
   const __nv_bfloat16* Dh;      // F'(re_t), blocked layout (tc_recurrent.cuh)
-  const uint32_t* Sg;           // [T][NP/32][2][BP] sign masks of r_t
+  const uint32_t* Sg;           // [T][NP/32][2][BP] zero / sign-bit masks of r_t
   const float* grad_output;     // [T,B,N] or nullptr
   const float* coef_x;          // [B,T] or nullptr
   const float* coef_y;
