@@ -187,21 +187,21 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         const uint32_t stage = c.stage_base + (uint32_t)(warp - 4) * 2048u;
         const size_t dl_row_bytes = (size_t)dl_blocks * NP * 2;
         if constexpr (!GEN) {
+          // packed bf16 multiplies (one instruction per two elements): the action scalar is rounded to bf16 first
 #pragma unroll
           for (int s = 0; s < 2; ++s) {
             // row 0 of this warp's 32-row block, first of this thread's 32 columns, column block 0
             uint8_t* blk0 = reinterpret_cast<uint8_t*>(p.DL + ((size_t)t * p.BP + (b - lane)) * (3 * NP) + nq + 64 * s);
+            const uint32_t L2 = pack_bf16x2(L, L), R2 = pack_bf16x2(R, R);
             uint32_t o[16];
 #pragma unroll
             for (int w = 0; w < 16; ++w) {
-              const uint32_t d2 = packed[s * 16 + w];
-              o[w] = pack_bf16x2(L * bf16_lo(d2), L * bf16_hi(d2));
+              o[w] = mul_bf16x2(packed[s * 16 + w], L2);
             }
             store_rows_via_smem(stage, lane, o, blk0 + (size_t)NP * 2, dl_row_bytes);
 #pragma unroll
             for (int w = 0; w < 16; ++w) {
-              const uint32_t d2 = packed[s * 16 + w];
-              o[w] = pack_bf16x2(R * bf16_lo(d2), R * bf16_hi(d2));
+              o[w] = mul_bf16x2(packed[s * 16 + w], R2);
             }
             store_rows_via_smem(stage, lane, o, blk0 + (size_t)2 * NP * 2, dl_row_bytes);
           }

@@ -173,8 +173,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           // Sign masks of r_t for the backward's d|r|/dr (bit j = this thread's j-th neuron of the sub-slice): the sign
           // bits, shifted in with one instruction per element (first element ends up in bit 31, undone by one bit
           // reversal), and a mask of exact zeros (sign(0) = 0), which is only worked out when min_mag -- the smallest
-          // magnitude seen, as raw bits shifted left by one -- says there is one.
-          uint32_t dpk[16], negr = 0u, min_mag = 0xffffffffu;
+          // magnitude seen -- says there is one.
+          uint32_t dpk[16], negr = 0u;
+          float min_mag = 3.0e38f;
 #pragma unroll
           for (int j0 = 0; j0 < 32; j0 += 8) {
             float re[8], f[8], d[8];
@@ -200,9 +201,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               const float r = fmaf(alpha, f[e], beta * master[idx]);
               master[idx] = r;
               f[e] = r;
-              const uint32_t bits = __float_as_uint(r);
-              negr = __funnelshift_l(bits, negr, 1);  // (negr << 1) | sign bit of r
-              min_mag = min(min_mag, bits << 1);
+              negr = __funnelshift_l(__float_as_uint(r), negr, 1);  // (negr << 1) | sign bit of r
+              min_mag = fminf(min_mag, fabsf(r));
             }
             if (want_dec) {
               // the group's eight decode weights in four 16-byte shared-memory loads (same address in every lane)
@@ -228,7 +228,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             const int n32 = (nq + 64 * s) >> 5;
             store_blocked(p.Dh + blocked_offset(t, b, n32, p.BP, NP), lane, dpk);
             uint32_t zero = 0u;
-            if (min_mag == 0u) {  // an exact zero among the 32 (always so for padding columns): mark them
+            if (min_mag == 0.f) {  // an exact zero among the 32 (always so for padding columns): mark them
 #pragma unroll
               for (int j = 0; j < 32; ++j) zero |= (master[s * 32 + j] == 0.f ? 1u : 0u) << j;
             }
