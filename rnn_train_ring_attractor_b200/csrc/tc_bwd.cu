@@ -61,7 +61,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     const float J0 = p.J0, J1 = p.J1, alpha = p.alpha, beta = 1.f - p.alpha;
     const bool has_coef = p.coef_x != nullptr;
     const bool want_dA = p.dA_part != nullptr;
-    const bool padded = p.N != NP;  // some of the NP columns are padding
     const int rq = (2 * q) / C_::SLOTS;  // the K round this CTA's own chunks belong to
     FreePhases<NP, PAIR> freed;
     uint32_t g = 0;
@@ -282,7 +281,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                   cv = fmaf(k0, __uint_as_float(z0[j]), cv);
                   cv = fmaf(k1, __uint_as_float(z1[j]), cv);
                   cv = fmaf(k2, __uint_as_float(z2[j]), cv);
-                  master[idx] = (!padded || nq + 64 * s + c16 * 16 + j < p.N) ? cv : 0.f;
+                  master[idx] = cv;  // padding columns need no masking: their F' is zero, so their delta is
                 }
               }
               release_accumulator<NP, PAIR>(c, (int)acc, lane);
@@ -336,7 +335,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               cv = fmaf(J1, __uint_as_float(zo[j]), cv);
               cv = fmaf(L, __uint_as_float(zl[j]), cv);
               cv = fmaf(R, __uint_as_float(zr[j]), cv);
-              master[idx] = (!padded || nq + 64 * s + c16 * 16 + j < p.N) ? cv : 0.f;
+              master[idx] = cv;  // padding columns need no masking: their F' is zero, so their delta is
             }
           }
           release_accumulator<NP, PAIR>(c, s, lane);
