@@ -95,7 +95,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           if (p.colR >= 0) R = __ldg(at + p.colR);
         }
         uint32_t packed[32];
-        float px = 0.f, py = 0.f, pa = 0.f, c0 = 0.f;
+        f32x2 px2 = pk2(0.f, 0.f), py2 = pk2(0.f, 0.f);  // decode sums, even / odd columns apart
+        float pa = 0.f, c0 = 0.f;
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
           // The pre-activation of this thread's 32 neurons of sub-slice s.  Two active columns: one accumulator holds
@@ -176,46 +177,61 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           // magnitude seen -- says there is one.
           uint32_t dpk[16], negr = 0u;
           float min_mag = 3.0e38f;
+          const f32x2 J1p = pk2(J1, J1), Lp = pk2(L, L), Rp = pk2(R, R), c0p = pk2(c0, c0), alphap = pk2(alpha, alpha),
+                      betap = pk2(beta, beta);
 #pragma unroll
           for (int j0 = 0; j0 < 32; j0 += 8) {
-            float re[8], f[8], d[8];
+            // eight neurons as four packed pairs
+            f32x2 re2[4], f2[4], d2[4];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
+            for (int i = 0; i < 4; ++i) {
+              const int e = j0 + 2 * i;
               if constexpr (GEN) {
-                re[e] = re_all[j0 + e];
+                re2[i] = pk2(re_all[e], re_all[e + 1]);
               } else {
-                float v = fmaf(J1, __uint_as_float(yo[j0 + e]), c0);
-                v = fmaf(L, __uint_as_float(yl[j0 + e]), v);
-                re[e] = fmaf(R, __uint_as_float(yr[j0 + e]), v);
+                f32x2 v = fma2(J1p, pk2u(yo[e], yo[e + 1]), c0p);
+                v = fma2(Lp, pk2u(yl[e], yl[e + 1]), v);
+                re2[i] = fma2(Rp, pk2u(yr[e], yr[e + 1]), v);
               }
             }
-            act_group<ACT, 8>(re, f, d);
+            act_group2<ACT, 8>(re2, f2, d2);
+            float f[8], d[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              upk2(f2[i], f[2 * i], f[2 * i + 1]);
+              upk2(d2[i], d[2 * i], d[2 * i + 1]);
+            }
             if (padded) {  // neurons beyond N stay at zero (their master state is zero): one uniform branch per group
 #pragma unroll
               for (int e = 0; e < 8; ++e)
                 if (nq + 64 * s + j0 + e >= p.N) { f[e] = 0.f; d[e] = 0.f; }
             }
 #pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int idx = s * 32 + j0 + 2 * i;
+              const f32x2 r2 = fma2(alphap, pk2(f[2 * i], f[2 * i + 1]), mul2(betap, pk2(master[idx], master[idx + 1])));
+              upk2(r2, master[idx], master[idx + 1]);
+              f[2 * i] = master[idx];
+              f[2 * i + 1] = master[idx + 1];
+            }
+#pragma unroll
             for (int e = 0; e < 8; ++e) {
-              const int idx = s * 32 + j0 + e;
-              const float r = fmaf(alpha, f[e], beta * master[idx]);
-              master[idx] = r;
-              f[e] = r;
-              negr = __funnelshift_l(__float_as_uint(r), negr, 1);  // (negr << 1) | sign bit of r
-              min_mag = fminf(min_mag, fabsf(r));
+              negr = __funnelshift_l(__float_as_uint(f[e]), negr, 1);  // (negr << 1) | sign bit of r
+              min_mag = fminf(min_mag, fabsf(f[e]));
             }
             if (want_dec) {
               // the group's eight decode weights in four 16-byte shared-memory loads (same address in every lane)
               const float4* up = reinterpret_cast<const float4*>(uv + 64 * s + 32 * h + j0);
               const float4* vp = reinterpret_cast<const float4*>(uv + 128 + 64 * s + 32 * h + j0);
               const float4 u0 = up[0], u1 = up[1], v0 = vp[0], v1 = vp[1];
-              const float uu[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-              const float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+              const f32x2 uu[4] = {pk2(u0.x, u0.y), pk2(u0.z, u0.w), pk2(u1.x, u1.y), pk2(u1.z, u1.w)};
+              const f32x2 vv[4] = {pk2(v0.x, v0.y), pk2(v0.z, v0.w), pk2(v1.x, v1.y), pk2(v1.z, v1.w)};
 #pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                px = fmaf(f[e], uu[e], px);
-                py = fmaf(f[e], vv[e], py);
-                pa += fabsf(f[e]);
+              for (int i = 0; i < 4; ++i) {
+                const f32x2 r2 = pk2(f[2 * i], f[2 * i + 1]);
+                px2 = fma2(r2, uu[i], px2);
+                py2 = fma2(r2, vv[i], py2);
+                pa += fabsf(f[2 * i]) + fabsf(f[2 * i + 1]);
               }
             }
 #pragma unroll
@@ -279,8 +295,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         }
         if (want_dec) {
           float* dp = p.dec_part + ((size_t)slot * 3 * T + t) * p.BP + b;
-          dp[0] = px;
-          dp[(size_t)T * p.BP] = py;
+          float pxa, pxb, pya, pyb;
+          upk2(px2, pxa, pxb);
+          upk2(py2, pya, pyb);
+          dp[0] = pxa + pxb;
+          dp[(size_t)T * p.BP] = pya + pyb;
           dp[(size_t)2 * T * p.BP] = pa;
         }
       }

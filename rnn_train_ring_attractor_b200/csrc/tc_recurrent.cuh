@@ -195,6 +195,38 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
+// ---- packed fp32 pairs (fma.rn.f32x2 and friends: one instruction for two elements, same rounding as the scalar
+// forms).  The epilogues are bound by their instruction count, not by the fp32 pipe.
+using f32x2 = unsigned long long;
+__device__ __forceinline__ f32x2 pk2(float a, float b) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 pk2u(uint32_t a, uint32_t b) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ void upk2(f32x2 v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// F(x) and F'(x) for G/2 packed pairs (G even); same formulas as act_group below, the polynomial and the products in
+// packed form, the special-function evaluations per element.
+template <int ACT, int G>
+__device__ __forceinline__ void act_group2(const f32x2* x2, f32x2* f2, f32x2* d2);
+
 // F(x) and F'(x) for a group of G independent elements, written stage by stage over the group so that the
 // G dependency chains interleave (the epilogue runs with two warps per scheduler: without instruction-level
 // parallelism inside the thread it is latency-bound).  Evaluation error is far below bf16 resolution.
@@ -250,6 +282,55 @@ __device__ __forceinline__ void act_group(const float* x, float* f, float* d) {
   }
 }
 
+
+template <int ACT, int G>
+__device__ __forceinline__ void act_group2(const f32x2* x2, f32x2* f2, f32x2* d2) {
+  constexpr int P = G / 2;
+  if constexpr (ACT == RINGRNN_ACT_GELU) {
+    float xs[G], t[G], e[G];
+#pragma unroll
+    for (int i = 0; i < P; ++i) upk2(x2[i], xs[2 * i], xs[2 * i + 1]);
+#pragma unroll
+    for (int i = 0; i < G; ++i) t[i] = __fdividef(1.f, fmaf(0.3275911f * 0.70710678118654752f, fabsf(xs[i]), 1.f));
+    const f32x2 kexp = pk2(-0.5f * 1.4426950408889634f, -0.5f * 1.4426950408889634f);
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      float a, b;
+      upk2(mul2(mul2(x2[i], x2[i]), kexp), a, b);
+      e[2 * i] = exp2f(a);
+      e[2 * i + 1] = exp2f(b);
+    }
+    // -poly(t) * t, Abramowitz-Stegun 7.1.26 with negated coefficients so that erf = 1 + (that) * e
+    const f32x2 c1 = pk2(-1.061405429f, -1.061405429f), c2 = pk2(1.453152027f, 1.453152027f),
+                c3 = pk2(-1.421413741f, -1.421413741f), c4 = pk2(0.284496736f, 0.284496736f),
+                c5 = pk2(-0.254829592f, -0.254829592f), one = pk2(1.f, 1.f), half = pk2(0.5f, 0.5f),
+                kphi = pk2(0.3989422804014327f, 0.3989422804014327f);
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      const f32x2 t2 = pk2(t[2 * i], t[2 * i + 1]), e2 = pk2(e[2 * i], e[2 * i + 1]);
+      f32x2 poly = fma2(t2, c1, c2);
+      poly = fma2(t2, poly, c3);
+      poly = fma2(t2, poly, c4);
+      poly = fma2(t2, poly, c5);
+      poly = mul2(poly, t2);
+      float ea, eb;
+      upk2(fma2(poly, e2, one), ea, eb);  // erf(|x| / sqrt 2)
+      const f32x2 cdf = fma2(half, pk2(copysignf(ea, xs[2 * i]), copysignf(eb, xs[2 * i + 1])), half);
+      f2[i] = mul2(x2[i], cdf);
+      d2[i] = fma2(mul2(x2[i], kphi), e2, cdf);
+    }
+  } else {
+    float x[G], f[G], d[G];
+#pragma unroll
+    for (int i = 0; i < P; ++i) upk2(x2[i], x[2 * i], x[2 * i + 1]);
+    act_group<ACT, G>(x, f, d);
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      f2[i] = pk2(f[2 * i], f[2 * i + 1]);
+      d2[i] = pk2(d[2 * i], d[2 * i + 1]);
+    }
+  }
+}
 
 // ---- per-CTA context and the roles both directions share -------------------------------------------------------
 template <int NP, bool PAIR>
