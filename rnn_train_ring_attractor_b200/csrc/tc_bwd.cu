@@ -27,6 +27,10 @@ __global__ void __launch_bounds__(THREADS, 1)
 bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmDL, const TcBwdParams p) {
   using C_ = Cfg<NP, PAIR>;
   static_assert(!GEN || (C_::ROUNDS == 1 && !PAIR), "weight groups: one K round, single CTAs");
+  // Carry and delta arithmetic on packed fp32 pairs: fewer instructions, a few more registers.  It pays where the
+  // epilogue is the longer part of a step (measured: -9 % at N = 256, -8 % at N = 128) and costs 1.5 % at N = 512,
+  // where this kernel sits at its register limit.
+  constexpr bool PACKED = NP <= 256;
   extern __shared__ uint8_t smem_raw[];
   const Ctx<NP, PAIR> c = setup_cta<NP, PAIR>(smem_raw, p.dec_u, p.dec_v, p.N, p.status);
   const int ng = GEN ? p.ng : 1;
@@ -133,6 +137,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           }
         }
         uint32_t packed[32];
+        const f32x2 cxp = pk2(cx, cx), cyp = pk2(cy, cy), onep = pk2(1.f, 1.f), alphap = pk2(alpha, alpha);
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
           // d|r|/dr = sign(r_t) is applied below as +cs or -cs by the sign bit alone (two instructions per element);
@@ -156,23 +161,36 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               vv[0] = v0.x; vv[1] = v0.y; vv[2] = v0.z; vv[3] = v0.w; vv[4] = v1.x; vv[5] = v1.y; vv[6] = v1.z; vv[7] = v1.w;
             }
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-              float dl[2];
-#pragma unroll
-              for (int e = 0; e < 2; ++e) {
-                const int j = v * 8 + w * 2 + e;
-                const int idx = s * 32 + j;
-                float gg = master[idx];
+            for (int w = 0; w < 4; ++w) {  // two neurons at a time
+              const int j = v * 8 + w * 2;
+              const int idx = s * 32 + j;
+              if constexpr (PACKED) {
+                f32x2 gg = pk2(master[idx], master[idx + 1]);
                 if (has_coef) {
-                  gg = fmaf(cx, uu[w * 2 + e], gg);
-                  gg = fmaf(cy, vv[w * 2 + e], gg);
-                  gg += (mneg[s] & (1u << j)) ? -cs : cs;  // + cs * sign(r_t); exact zeros were pre-compensated
+                  gg = fma2(cxp, pk2(uu[w * 2], uu[w * 2 + 1]), gg);
+                  gg = fma2(cyp, pk2(vv[w * 2], vv[w * 2 + 1]), gg);
+                  // + cs * sign(r_t) by the sign bit; exact zeros were pre-compensated
+                  gg = fma2(onep, pk2((mneg[s] & (1u << j)) ? -cs : cs, (mneg[s] & (2u << j)) ? -cs : cs), gg);
                 }
-                master[idx] = gg;
-                const float dact = e ? bf16_hi(dw[w]) : bf16_lo(dw[w]);
-                dl[e] = alpha * dact * gg;
+                upk2(gg, master[idx], master[idx + 1]);
+                float d0, d1;
+                upk2(mul2(mul2(alphap, pk2(bf16_lo(dw[w]), bf16_hi(dw[w]))), gg), d0, d1);
+                packed[s * 16 + v * 4 + w] = pack_bf16x2(d0, d1);
+              } else {
+                float dl[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                  float gg = master[idx + e];
+                  if (has_coef) {
+                    gg = fmaf(cx, uu[w * 2 + e], gg);
+                    gg = fmaf(cy, vv[w * 2 + e], gg);
+                    gg += (mneg[s] & (1u << (j + e))) ? -cs : cs;  // + cs * sign(r_t); exact zeros were pre-compensated
+                  }
+                  master[idx + e] = gg;
+                  dl[e] = alpha * (e ? bf16_hi(dw[w]) : bf16_lo(dw[w])) * gg;
+                }
+                packed[s * 16 + v * 4 + w] = pack_bf16x2(dl[0], dl[1]);
               }
-              packed[s * 16 + v * 4 + w] = pack_bf16x2(dl[0], dl[1]);
             }
           }
         }
@@ -308,6 +326,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             tmem_ld_wait();
             c0 = J0 * __uint_as_float(sraw);
           }
+          const f32x2 betap = pk2(beta, beta), c0p = pk2(c0, c0), J1p = pk2(J1, J1), Lp = pk2(L, L), Rp = pk2(R, R);
 #pragma unroll
           for (int c16 = 0; c16 < 2; ++c16) {
             uint32_t zo[16], zl[16], zr[16];
@@ -328,14 +347,27 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 dAr = fmaf(rp, __uint_as_float(zr[j]), dAr);
               }
             }
+            // padding columns need no masking: their F' is zero, so their delta is
+            if constexpr (PACKED) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int idx = s * 32 + c16 * 16 + j;
-              float cv = fmaf(beta, master[idx], c0);
-              cv = fmaf(J1, __uint_as_float(zo[j]), cv);
-              cv = fmaf(L, __uint_as_float(zl[j]), cv);
-              cv = fmaf(R, __uint_as_float(zr[j]), cv);
-              master[idx] = cv;  // padding columns need no masking: their F' is zero, so their delta is
+              for (int i = 0; i < 8; ++i) {
+                const int idx = s * 32 + c16 * 16 + 2 * i;
+                f32x2 cv = fma2(betap, pk2(master[idx], master[idx + 1]), c0p);
+                cv = fma2(J1p, pk2u(zo[2 * i], zo[2 * i + 1]), cv);
+                cv = fma2(Lp, pk2u(zl[2 * i], zl[2 * i + 1]), cv);
+                cv = fma2(Rp, pk2u(zr[2 * i], zr[2 * i + 1]), cv);
+                upk2(cv, master[idx], master[idx + 1]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int idx = s * 32 + c16 * 16 + j;
+                float cv = fmaf(beta, master[idx], c0);
+                cv = fmaf(J1, __uint_as_float(zo[j]), cv);
+                cv = fmaf(L, __uint_as_float(zl[j]), cv);
+                cv = fmaf(R, __uint_as_float(zr[j]), cv);
+                master[idx] = cv;
+              }
             }
           }
           release_accumulator<NP, PAIR>(c, s, lane);
