@@ -4,8 +4,11 @@
 
 Metric: fwd+bwd sample-timesteps/s (= B*T / step time) at N=512, B=4096, T=512, GELU (workload "c3").
 A step is one pass of the hot path over one synthetic batch: forward recurrence, decode + loss, reverse-time
-recurrence, weight-gradient products and (N > 1) one all-reduce of the gradient buffer.  With N GPUs every
-rank runs the full per-GPU batch (weak scaling) unless --scaling strong shards the one global batch.
+recurrence, weight-gradient products and (N > 1) one all-reduce of the gradient buffer.  With N GPUs the ONE global
+batch of the configuration (4096 samples for c3, generated from one seed) is sharded evenly by rows, rank r taking
+rows [r*B/N, (r+1)*B/N) -- strong scaling, as the configuration is worded; --scaling weak gives every rank a full
+per-GPU batch instead.  The line carries the loss and checksums of the all-reduced gradients, which are the same
+numbers at every N up to fp32 summation order.
 
 `value`  : inputs already resident in HBM, timed with CUDA events on the launching stream.
 `e2e`    : the same step through the public Python API with inputs in pinned HOST memory (H2D copies and the
@@ -41,6 +44,7 @@ WORKLOADS = {
 }
 # DRAM bytes (read + write) per sample-timestep of each bf16-mode kernel at N=512, from the ncu captures summarised
 # under profiles/ (taken at T=64, B=4096; traffic is proportional to B*T).  None = no capture for that kernel/mode.
+NCU_CAPTURE_SOURCE = "ncu captures at T=64 summarised in profiles/{fwd,bwd}_tc_kernel_c3_T64.md, gemm_tc_kernel_dw_c3_T64.md"
 NCU_DRAM_BYTES_PER_SAMPLE_STEP = {
     ("bf16", 512): {"fwd_recurrent": (16.50e6 + 544.22e6) / (4096 * 64), "bwd_recurrent": (309.06e6 + 750.17e6) / (4096 * 64),
                     "dw_product": (1074.0e6 + 3.95e6) / (4096 * 64)},
@@ -55,7 +59,8 @@ def measured_peaks():
         with open(path) as f:
             d = json.load(f)
         return d, "measured"
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+    # no driver-written file: an earlier measurement on the same pool (burst figure only)
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
 
 
 class ClockSampler:
@@ -325,14 +330,20 @@ def run_ours(args, wl):
     L = _lib.lib()
 
     N, T, act = wl["N"], wl["T"], wl["act"]
-    if args.scaling == "strong":
+    scaling = args.scaling or ("weak" if "defined_on" in wl else "strong")
+    if scaling == "strong":
+        if wl["B"] % world:
+            raise RuntimeError(f"global batch {wl['B']} does not divide over {world} ranks")
         B_global, B_local = wl["B"], wl["B"] // world
     else:
         B_global, B_local = wl["B"] * world, wl["B"]
     prec_code = choose_precision(B_local, T, N, 2, _lib.ACT[act], 2, args.precision)
     prec = "bf16" if prec_code == 1 else "fp32"
 
-    host = benchmark_inputs(N, B_local, T, seed=1000 + rank, max_av=wl["max_av"])
+    # one global batch and one set of weights from seed 0 on every rank; the rank keeps its rows
+    host = benchmark_inputs(N, B_global, T, seed=0, max_av=wl["max_av"])
+    for k in ("A", "r_init", "target"):
+        host[k] = dp.shard_rows(host[k], rank, world)
     pinned = {k: host[k].pin_memory() for k in ("A", "r_init", "target")}
     Wa, Wo = host["Wa"].to(dev), host["Wo"].to(dev)
     resident = tuple(pinned[k].to(dev) for k in ("A", "r_init", "target"))
@@ -362,8 +373,11 @@ def run_ours(args, wl):
 
     # ---- device-resident value --------------------------------------------------------------------------
     for _ in range(max(1, args.warmup)):
-        loss, _ = step(resident)
+        loss, grads = step(resident)
     torch.cuda.synchronize()
+    # the all-reduced gradients of the one global batch: the same at every GPU count up to fp32 summation order
+    checksum = {"dWo_norm": float(grads["dWo"].double().norm()), "dWa_norm": float(grads["dWa"].double().norm()),
+                "dWo_sum": float(grads["dWo"].double().sum()), "dJ0": float(grads["dJ"][0]), "dJ1": float(grads["dJ"][1])}
     L.ringrnn_timing_reset()
     L.ringrnn_timing_enable(1)
     sampler = ClockSampler(local_rank)
@@ -418,20 +432,32 @@ def run_ours(args, wl):
 
     # ---- roofline of the dominant kernel class ----------------------------------------------------------
     peaks, peak_src = measured_peaks()
-    flops_per_launch = 6.0 * N * N * B_local * T  # each of: forward contraction, delta propagation, dW products
+    # Algorithmic work of each kernel class per step: 6*N*N flop per sample-timestep for each of the forward
+    # contraction, the delta propagation and the weight-gradient products.  With checkpoints a class runs in several
+    # launches per step (one per stretch, plus the recompute in the forward class, whose work is not counted):
+    # achieved = the class's algorithmic flops per step / the class's time per step.
+    flops_per_class = 6.0 * N * N * B_local * T
     cand = {k: v for k, v in kern.items() if k in ("fwd_recurrent", "bwd_recurrent", "dw_product") and v[1] > 0}
     dom = max(cand, key=lambda k: cand[k][0]) if cand else None
     roof = None
     if dom:
-        ms_launch = cand[dom][0] / cand[dom][1]
-        achieved = flops_per_launch / (ms_launch * 1e-3) / 1e12
-        peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
-        per_unit = NCU_DRAM_BYTES_PER_SAMPLE_STEP.get((prec, N), {}).get(dom)
-        traffic = per_unit * B_local * T if per_unit is not None else None
+        ms_class = cand[dom][0] / args.steps
+        launches_per_step = cand[dom][1] / args.steps
+        achieved = flops_per_class / (ms_class * 1e-3) / 1e12
+        sustained = "bf16_tflops_sustained" in peaks
+        peak = float(peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"])
+        cap = NCU_DRAM_BYTES_PER_SAMPLE_STEP.get((prec, N), {}).get(dom) if not args.ckpt_every else None
+        traffic = cap * B_local * T / launches_per_step if cap is not None else None
         roof = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": traffic, "peak_source": f"{peak_src} (sustained bf16 GEMM)",
-                "ms_per_launch": ms_launch,
-                "kernels_ms_per_step": {k: v[0] / args.steps for k, v in kern.items() if v[1] > 0}}
+                "frac": achieved / peak, "traffic": traffic,
+                "traffic_source": NCU_CAPTURE_SOURCE if traffic is not None else None,
+                "peak_source": f"{peak_src} ({'sustained' if sustained else 'burst'} bf16 GEMM)",
+                "ms_per_launch": ms_class / launches_per_step, "launches_per_step": launches_per_step,
+                "kernels_ms_per_step": {k: v[0] / args.steps for k, v in kern.items() if v[1] > 0},
+                # the recurrence is sequential: time per timestep of each recurrent kernel, the floor that batch
+                # sharding cannot lower
+                "us_per_timestep": {k: 1e3 * cand[k][0] / args.steps / T for k in ("fwd_recurrent", "bwd_recurrent")
+                                    if k in cand}}
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
@@ -441,7 +467,7 @@ def run_ours(args, wl):
     value = B_global * T / (ms_step * 1e-3)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
         "dtype": "bf16" if prec == "bf16" else "f32", "data": "synthetic",
         "config": {"workload": f"{args.workload}: N={N}, B={B_local} per GPU, T={T}, {act}, alpha=0.1, "
                                f"fused fwd+loss+bwd, precision mode {prec}"
@@ -449,7 +475,7 @@ def run_ours(args, wl):
                                   if args.ckpt_every else "")
                                + (f" (the configuration is defined on {wl['defined_on']} GPUs, global batch "
                                   f"{wl['B'] * wl['defined_on']}; this run has {world})"
-                                  if wl.get("defined_on", world) != world and args.scaling == "weak" else ""),
+                                  if wl.get("defined_on", world) != world and scaling == "weak" else ""),
                    "global_batch": B_global, "parallelism": f"dp{world}",
                    "l2": "working set (saved states + delta, several GB) exceeds the 126 MB L2; no flush needed"},
         "e2e": {"value": B_global * T / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
@@ -457,6 +483,7 @@ def run_ours(args, wl):
                 "how": "public API ring_rnn_fused via dp.train_step; inputs in pinned host memory, H2D double-buffered on a "
                        "copy stream, loss read back every step"},
         "gpu_launches": launches, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "loss": loss_value,
+        "grad_checksum": checksum,
     }
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -471,7 +498,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + ["published"])
     ap.add_argument("--precision", default="auto", choices=["auto", "bf16", "fp32"])
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--scaling", default=None, choices=["weak", "strong"],
+                    help="default: strong (the one global batch sharded over the GPUs); weak for the workload that is "
+                         "defined by its per-GPU shard (c4)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--seq-len", type=int, default=0, help="override T (profiling on a smaller case of the same kernels)")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling)")

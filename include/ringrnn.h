@@ -4,7 +4,8 @@
  * Plain pointers and sizes only; every pointer named "device" is CUDA device memory owned by
  * the caller, including all scratch ("workspace") and saved-for-backward storage, whose sizes
  * ringrnn_workspace_bytes() reports.  No entry point allocates device memory, exits the process
- * or throws: each returns a RINGRNN_* status.  Calls are asynchronous on `stream` (a cudaStream_t
+ * or throws: each returns a RINGRNN_* status.  (Host side, the library keeps one 256-byte block of pinned
+ * host memory for the deferred status reports described at RingRnnFwdArgs, allocated once on first use.)  Calls are asynchronous on `stream` (a cudaStream_t
  * passed as void*; NULL = the legacy default stream) and may come from any host thread.
  *
  * Each declaration cites the interface of the reference project (chongxi/rnn_train_ring_attractor,
@@ -28,7 +29,7 @@ enum {
   RINGRNN_ERR_WORKSPACE = 3,   /* workspace / saved buffer missing, misaligned or too small    */
   RINGRNN_ERR_CUDA = 4,        /* a CUDA runtime call failed (see ringrnn_last_cuda_error)     */
   RINGRNN_ERR_UNSUPPORTED = 5, /* valid request that this precision mode cannot serve          */
-  RINGRNN_ERR_DEVICE = 6,      /* a kernel reported a bounded wait that ran out                */
+  RINGRNN_ERR_DEVICE = 6,      /* a kernel of an EARLIER call reported a bounded wait that ran out */
   RINGRNN_ERR_TOO_LARGE = 7    /* size exceeds the capacity of the library's built-in scratch  */
 };
 
@@ -50,7 +51,8 @@ enum { RINGRNN_WS_FWD = 0, RINGRNN_WS_SAVED = 1, RINGRNN_WS_BWD = 2 };
  *   A[B,T,a_dim], Wa[a_dim,N,N], Wo[N,N], r_init[B,N], all fp32, contiguous, device memory.
  * n_active / active_cols name the columns of A that are not identically zero (the root training
  * script pads the L/R signal to 16 columns with zeros, train_general_ring_no_gain.py:200-223);
- * n_active < 0 means "all a_dim columns".  Gradients of skipped columns are exactly zero.
+ * n_active < 0 means "all a_dim columns" (the fp32 mode then takes any a_dim; the bf16 mode at most
+ * RINGRNN_MAX_ACTIVE active columns).  Gradients of skipped columns are exactly zero.
  * ckpt_every = K > 0 (bf16 mode, persistent kernels): the forward keeps only the fp32 state every K steps and the
  * backward recomputes each stretch of K steps from its checkpoint before it propagates through it -- the saved
  * storage shrinks from two bf16 tensors of T*B*N to T/K fp32 states of B*N, for one extra forward pass.  0 = keep every
@@ -78,7 +80,14 @@ typedef struct RingRnnProblem {
  *   dec_u, dec_v  [N] fp32 in, required when any dec_* output is requested
  *   final_state   [B,N] fp32 out, r_T (NULL = skip)
  *   workspace     RINGRNN_WS_FWD bytes of scratch
- *   status        optional device int, set non-zero if a bounded device-side wait ran out */
+ *   status        optional device int that the CALLER has set to zero: the bf16-mode kernels set it non-zero if a
+ *                 bounded device-side wait ran out, and once it is non-zero every later wait of kernels that share the
+ *                 word gives up at once (NULL = the library uses, and zeroes, the first word of `workspace`).
+ * Error reporting is deferred, because the call returns before its kernels have run (the reference synchronises and
+ * exits instead, cpp/cuda_common.cuh:30-39): the status word is copied to the host behind the kernels, and the NEXT
+ * ringrnn_fwd / ringrnn_bwd call of the process returns RINGRNN_ERR_DEVICE if a word that has arrived is non-zero --
+ * the results of the launches since the last successful report are then invalid.  ringrnn_device_status() does the same
+ * check on demand, e.g. right after the caller's own synchronisation. */
 typedef struct RingRnnFwdArgs {
   RingRnnProblem p;
   float* bump_history;
@@ -162,6 +171,21 @@ int ringrnn_bwd_cuda(const void* grad_output, const void* A, const void* Wa, flo
                      int N, int a_dim, int seq_len, int batch_size, int activation_type, int precision,
                      const void* saved, size_t saved_bytes, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Deferred device-side failures (see RingRnnFwdArgs).  Returns RINGRNN_ERR_DEVICE and stores the kernel's code in *code
+ * (may be NULL) if a bf16-mode launch whose status word has reached the host abandoned a bounded wait; RINGRNN_OK and 0
+ * otherwise.  Reading clears the report.  Never synchronises: call it after a stream or device synchronisation of your
+ * own to learn about everything launched before it.  ringrnn_last_device_code(): the code of the most recent report
+ * delivered to this host thread.  Replaces CHECK_CUDA_ERROR after each kernel (cpp/cuda_common.cuh:30-39,
+ * cpp/fwd.cu:49). */
+int ringrnn_device_status(int* code);
+int ringrnn_last_device_code(void);
+
+/* Self-test of the bounded wait (no counterpart in the reference): launches one thread that waits for an event that
+ * never happens, with a limit of `limit_cycles` SM cycles (<= 4e9) instead of the kernels' ~1 s.  The kernel ends
+ * normally, `*status` (device int, zeroed by the caller) receives `code` (non-zero), and the report is queued like any
+ * other, so the next ringrnn_fwd / ringrnn_bwd / ringrnn_device_status sees RINGRNN_ERR_DEVICE. */
+int ringrnn_selftest_wait(long long limit_cycles, int code, int* status, void* stream);
+
 /* Decode + loss on the [B,T] scalars the forward emits.  Replaces the [B,T,N]-sized chain
  * `bump @ W_delta7`, max-normalise (train_general_ring_no_gain.py:113-116), cosine_similarity_loss
  * (train/train_ring_attractor.py:190-220) and bump_amplitude_loss (:275-298).
@@ -181,7 +205,9 @@ int ringrnn_angle_loss(int B, int T, const float* dec_x, const float* dec_y, con
  * that may not allocate device memory at the point where they need the loss: a serving process whose
  * memory is owned entirely by its framework's pool, so that a raw allocation would fail or fragment it, or a
  * latency-critical loop that cannot afford the device-wide synchronisation an allocation implies.  The call
- * itself performs no cudaMalloc / cudaFree and calls no allocating library routine.
+ * itself performs no cudaMalloc / cudaFree and calls no allocating library routine -- with one exception you
+ * control: while ringrnn_timing_enable(1) is in force every launch of this library, this one included, creates a
+ * pair of CUDA events (cudaEventCreate); leave timing off where that matters.
  *   - B > RINGRNN_STATIC_LOSS_MAX_B is rejected with RINGRNN_ERR_TOO_LARGE before anything is launched.
  *   - The first call on each device looks up the array's device address (once per device, with that device
  *     current); make that first call outside any stream capture.

@@ -14,6 +14,7 @@ ACT = {"relu": 0, "gelu": 1, "tanh": 2, "silu": 3}  # cpp/ring_rnn_cuda.py:63
 PREC = {"fp32": 0, "bf16": 1}
 WS_FWD, WS_SAVED, WS_BWD = 0, 1, 2
 ERR_UNSUPPORTED = 5
+ERR_DEVICE = 6
 ERR_TOO_LARGE = 7
 STATIC_LOSS_MAX_B = 65536
 
@@ -67,6 +68,9 @@ SYMBOLS = {
                                             C.c_void_p, C.c_void_p]),
     "ringrnn_clip_adam": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_float, C.c_float,
                                     C.c_float, C.c_float, C.c_int, C.c_float, C.c_void_p, C.c_void_p]),
+    "ringrnn_device_status": (C.c_int, [C.POINTER(C.c_int)]),
+    "ringrnn_last_device_code": (C.c_int, []),
+    "ringrnn_selftest_wait": (C.c_int, [C.c_longlong, C.c_int, C.c_void_p, C.c_void_p]),
     "ringrnn_launch_count": (C.c_longlong, []),
     "ringrnn_timing_slots": (C.c_int, []),
     "ringrnn_timing_name": (C.c_char_p, [C.c_int]),
@@ -108,7 +112,17 @@ def check(status):
         text = L.ringrnn_strerror(status).decode()
         if status == 4:
             text += ": " + L.ringrnn_last_cuda_error_string().decode()
+        if status == ERR_DEVICE:
+            text += (f" (kernel code {L.ringrnn_last_device_code()}): the results of the launches before this call are "
+                     "invalid")
         raise RingRnnError(status, text)
+
+
+def raise_if_device_error():
+    """Raise RingRnnError(6) if a bf16-mode launch whose status word has reached the host abandoned a bounded wait.
+    Never synchronises: call it right after a synchronisation of your own (the read-back of a loss, say) to cover
+    everything launched before it.  The library makes the same check on entry to every forward / backward call."""
+    check(lib().ringrnn_device_status(None))
 
 
 def make_problem(B, T, N, a_dim, act, prec, J0, J1, alpha, A, Wa, Wo, r_init, active=None, ckpt_every=0):
@@ -118,7 +132,10 @@ def make_problem(B, T, N, a_dim, act, prec, J0, J1, alpha, A, Wa, Wo, r_init, ac
     p.activation, p.precision = act, prec
     p.J0, p.J1, p.alpha = float(J0), float(J1), float(alpha)
     p.A, p.Wa, p.Wo, p.r_init = A, Wa, Wo, r_init
-    if active is None:
+    if active is None or len(active) > MAX_ACTIVE:
+        # all columns (the list holds MAX_ACTIVE entries; beyond that only "all" can be expressed, fp32 mode only)
+        if active is not None and len(active) != a_dim:
+            raise ValueError(f"more than {MAX_ACTIVE} active action columns must be all {a_dim} of them")
         p.n_active = -1
     else:
         p.n_active = len(active)
@@ -142,8 +159,9 @@ CHECK_DEVICE_STATUS = os.environ.get("RINGRNN_CHECK", "0") == "1"
 
 
 def check_device_status(workspace, what):
-    """With RINGRNN_CHECK=1: synchronise and raise if a bf16-mode kernel abandoned a bounded wait (the first word of
-    its scratch buffer is the status word).  Off by default because it costs a device synchronisation per call."""
+    """With RINGRNN_CHECK=1: synchronise and raise at once if a bf16-mode kernel abandoned a bounded wait (the first
+    word of its scratch buffer is the status word).  Without it the failure is reported by the NEXT library call or
+    by raise_if_device_error(), with no synchronisation (the status word travels to the host behind the kernels)."""
     if not CHECK_DEVICE_STATUS:
         return
     import torch

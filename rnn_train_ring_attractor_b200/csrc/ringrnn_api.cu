@@ -6,8 +6,24 @@
 #include <vector>
 
 #include "ringrnn_common.cuh"
+#include "tc_ptx.cuh"
 
 namespace ringrnn {
+
+// Self-test of the bounded wait every tensor-core kernel is built on: one thread waits, through the same mbar_wait(),
+// for a barrier phase that nothing will ever complete.  After `limit` cycles the wait gives up, records `code` in the
+// status word and the kernel ends normally.
+__global__ void wait_selftest_kernel(int* status, long long limit, int code) {
+  __shared__ alignas(8) unsigned long long bar;
+  __shared__ int dead;
+  if (threadIdx.x == 0) {
+    dead = 0;
+    tc::mbar_init(tc::smem_u32(&bar), 1);
+    tc::fence_mbar_init();
+    tc::WaitCtx w{&dead, status, limit};
+    (void)tc::mbar_wait(tc::smem_u32(&bar), 0, w, code);
+  }
+}
 
 static thread_local cudaError_t g_last_cuda_error = cudaSuccess;
 void set_last_cuda_error(cudaError_t e) { g_last_cuda_error = e; }
@@ -52,6 +68,49 @@ static void drain_timed_locked() {
   g_timed.clear();
 }
 
+// ---- deferred device status --------------------------------------------------------------------
+// The reference learns of a failed kernel at once, because it synchronises and exits (cpp/cuda_common.cuh:30-39).
+// Here a launch returns before its kernels run, so the status word they may set is copied, behind them on the same
+// stream, into a ring of pinned host words; every later entry into the library looks at the ring and reports a
+// non-zero word as RINGRNN_ERR_DEVICE.  No synchronisation anywhere.
+constexpr int STATUS_SLOTS = 64;
+static std::mutex g_status_mu;
+static volatile int* g_status_ring = nullptr;  // pinned host memory, STATUS_SLOTS words
+static int g_status_next = 0;
+static int g_status_sticky = 0;                // first unreported code
+
+int queue_status_report(const int* dev_status, cudaStream_t s) {
+  if (dev_status == nullptr) return RINGRNN_OK;
+  std::lock_guard<std::mutex> lk(g_status_mu);
+  if (g_status_ring == nullptr) {
+    void* h = nullptr;
+    RINGRNN_CUDA_TRY(cudaHostAlloc(&h, sizeof(int) * STATUS_SLOTS, cudaHostAllocPortable));
+    memset(h, 0, sizeof(int) * STATUS_SLOTS);
+    g_status_ring = static_cast<volatile int*>(h);
+  }
+  const int slot = g_status_next;
+  g_status_next = (g_status_next + 1) % STATUS_SLOTS;
+  if (g_status_ring[slot] != 0 && g_status_sticky == 0) g_status_sticky = g_status_ring[slot];
+  g_status_ring[slot] = 0;
+  RINGRNN_CUDA_TRY(cudaMemcpyAsync(const_cast<int*>(g_status_ring) + slot, dev_status, sizeof(int), cudaMemcpyDeviceToHost, s));
+  return RINGRNN_OK;
+}
+
+// first unreported non-zero status word that has arrived on the host (0 if none); clears what it returns
+static int take_device_status() {
+  std::lock_guard<std::mutex> lk(g_status_mu);
+  int code = g_status_sticky;
+  g_status_sticky = 0;
+  if (g_status_ring != nullptr)
+    for (int i = 0; i < STATUS_SLOTS; ++i)
+      if (g_status_ring[i] != 0) {
+        if (code == 0) code = g_status_ring[i];
+        g_status_ring[i] = 0;
+      }
+  return code;
+}
+static thread_local int g_last_device_code = 0;
+
 namespace {
 
 int check_problem(const RingRnnProblem& p) {
@@ -60,7 +119,9 @@ int check_problem(const RingRnnProblem& p) {
   if (p.precision != RINGRNN_PREC_FP32 && p.precision != RINGRNN_PREC_BF16) return RINGRNN_ERR_ARG;
   if (p.n_active > p.a_dim || p.n_active > RINGRNN_MAX_ACTIVE) return RINGRNN_ERR_ARG;
   if (p.ckpt_every < 0) return RINGRNN_ERR_ARG;
-  if (p.n_active < 0 && p.a_dim > RINGRNN_MAX_ACTIVE) return RINGRNN_ERR_UNSUPPORTED;
+  // more than RINGRNN_MAX_ACTIVE columns ("all columns", a_dim beyond the list's size): the fp32 mode takes them, as the
+  // reference's kernels take any a_dim (cpp/fwd.cu:21-50); the tensor-core modes do not
+  if (p.n_active < 0 && p.a_dim > RINGRNN_MAX_ACTIVE && p.precision != RINGRNN_PREC_FP32) return RINGRNN_ERR_UNSUPPORTED;
   for (int k = 0; k < p.n_active; ++k)
     if (p.active_cols[k] < 0 || p.active_cols[k] >= p.a_dim) return RINGRNN_ERR_ARG;
   return RINGRNN_OK;
@@ -79,7 +140,8 @@ DevProblem to_dev(const RingRnnProblem& p) {
   d.A = p.A; d.Wa = p.Wa; d.Wo = p.Wo; d.r_init = p.r_init;
   const int n = (p.n_active < 0) ? p.a_dim : p.n_active;
   d.n_mat = 1 + n;
-  for (int k = 0; k < n; ++k) d.cols[k] = (p.n_active < 0) ? k : p.active_cols[k];
+  d.all_cols = p.n_active < 0 ? 1 : 0;
+  for (int k = 0; k < n && k < RINGRNN_MAX_ACTIVE; ++k) d.cols[k] = (p.n_active < 0) ? k : p.active_cols[k];
   return d;
 }
 
@@ -137,12 +199,17 @@ extern "C" int ringrnn_fwd(const RingRnnFwdArgs* a, void* stream) {
   const bool want_dec = a->dec_x || a->dec_y || a->dec_ta;
   if (want_dec && (!a->dec_u || !a->dec_v)) return RINGRNN_ERR_ARG;
   if (!a->bump_history && !a->saved && !want_dec && !a->final_state) return RINGRNN_ERR_ARG;  // nothing to produce
+  if (const int code = take_device_status()) {  // an EARLIER launch abandoned a bounded wait: its results are invalid
+    g_last_device_code = code;
+    return RINGRNN_ERR_DEVICE;
+  }
   const DevProblem dp = to_dev(a->p);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (a->p.precision == RINGRNN_PREC_BF16) {
-    if (bf16_supported(a->p)) return bf16_forward(*a, dp, s);
-    if (stepwise_supported(a->p)) return stepwise_forward(*a, dp, s);
-    return RINGRNN_ERR_UNSUPPORTED;
+    if (!bf16_supported(a->p) && !stepwise_supported(a->p)) return RINGRNN_ERR_UNSUPPORTED;
+    rc = bf16_supported(a->p) ? bf16_forward(*a, dp, s) : stepwise_forward(*a, dp, s);
+    if (rc != RINGRNN_OK) return rc;
+    return queue_status_report(a->status != nullptr ? a->status : static_cast<const int*>(a->workspace), s);
   }
   return fp32_forward(*a, dp, s);
 }
@@ -156,12 +223,17 @@ extern "C" int ringrnn_bwd(const RingRnnBwdArgs* a, void* stream) {
   if (!a->grad_Wa || !a->grad_Wo) return RINGRNN_ERR_ARG;
   if (!a->grad_output && !a->coef_x) return RINGRNN_ERR_ARG;
   if (a->coef_x && (!a->coef_y || !a->coef_s || !a->dec_u || !a->dec_v)) return RINGRNN_ERR_ARG;
+  if (const int code = take_device_status()) {
+    g_last_device_code = code;
+    return RINGRNN_ERR_DEVICE;
+  }
   const DevProblem dp = to_dev(a->p);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (a->p.precision == RINGRNN_PREC_BF16) {
-    if (bf16_supported(a->p)) return bf16_backward(*a, dp, s);
-    if (stepwise_supported(a->p)) return stepwise_backward(*a, dp, s);
-    return RINGRNN_ERR_UNSUPPORTED;
+    if (!bf16_supported(a->p) && !stepwise_supported(a->p)) return RINGRNN_ERR_UNSUPPORTED;
+    rc = bf16_supported(a->p) ? bf16_backward(*a, dp, s) : stepwise_backward(*a, dp, s);
+    if (rc != RINGRNN_OK) return rc;
+    return queue_status_report(a->status != nullptr ? a->status : static_cast<const int*>(a->workspace), s);
   }
   return fp32_backward(*a, dp, s);
 }
@@ -204,6 +276,25 @@ extern "C" int ringrnn_bwd_cuda(const void* grad_output, const void* A, const vo
   a.workspace = workspace; a.workspace_bytes = workspace_bytes;
   return ringrnn_bwd(&a, stream);
 }
+
+extern "C" int ringrnn_selftest_wait(long long limit_cycles, int code, int* status, void* stream) {
+  if (status == nullptr || limit_cycles < 0 || limit_cycles > 4000000000LL || code == 0) return RINGRNN_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  {
+    LaunchScope ls(K_PREP, s);
+    wait_selftest_kernel<<<1, 32, 0, s>>>(status, limit_cycles, code);
+  }
+  RINGRNN_CUDA_TRY(cudaGetLastError());
+  return queue_status_report(status, s);
+}
+
+extern "C" int ringrnn_device_status(int* code) {
+  const int c = take_device_status();
+  if (c != 0) g_last_device_code = c;
+  if (code != nullptr) *code = c != 0 ? c : 0;
+  return c != 0 ? RINGRNN_ERR_DEVICE : RINGRNN_OK;
+}
+extern "C" int ringrnn_last_device_code(void) { return g_last_device_code; }
 
 extern "C" long long ringrnn_launch_count(void) { return g_launches.load(); }
 extern "C" int ringrnn_timing_slots(void) { return K_SLOTS; }

@@ -80,8 +80,16 @@ struct DevProblem {
   const float* Wo;      // [N,N]
   const float* r_init;  // [B,N]
   int n_mat;            // 1 + number of active action columns
+  int all_cols;         // non-zero: every column of A is active, column k is k (cols[] unused; a_dim may exceed its size)
   int cols[RINGRNN_MAX_ACTIVE];  // active action columns
 };
+// the k-th active action column
+__host__ __device__ __forceinline__ int active_col(const DevProblem& p, int k) { return p.all_cols ? k : p.cols[k]; }
+
+// Deferred report of a bounded device-side wait that ran out: queues a copy of the kernels' status word into pinned
+// host memory behind them on `s` (no synchronisation); the next ringrnn_fwd / ringrnn_bwd / ringrnn_device_status call
+// on this process looks at the words that have arrived.
+int queue_status_report(const int* dev_status, cudaStream_t s);
 
 // dJ0 / dJ1 from the unscaled Wo gradient (ringrnn_fp32.cu); scratch: GRAD_J_BLOCKS * 2 doubles
 constexpr int GRAD_J_BLOCKS = 128;

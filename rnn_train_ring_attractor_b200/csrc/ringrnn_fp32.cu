@@ -21,7 +21,7 @@ constexpr int FT = 256;      // threads per CTA in the recurrent kernels
 __global__ void transpose_weights_kernel(DevProblem p, float* __restrict__ WT) {
   __shared__ float tile[32][33];
   const int m = blockIdx.z;
-  const float* W = (m == 0) ? p.Wo : p.Wa + (size_t)p.cols[m - 1] * p.N * p.N;
+  const float* W = (m == 0) ? p.Wo : p.Wa + (size_t)active_col(p, m - 1) * p.N * p.N;
   float* O = WT + (size_t)m * p.N * p.N;
   const int j0 = blockIdx.x * 32, i0 = blockIdx.y * 32;
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
@@ -69,7 +69,7 @@ __device__ __forceinline__ void load_scales(const DevProblem& p, int b0, int t, 
   for (int idx = threadIdx.x; idx < p.n_mat * BT; idx += FT) {
     const int m = idx / BT, b = idx % BT;
     float v = p.J1;
-    if (m > 0) v = (b0 + b < p.B) ? __ldg(p.A + ((size_t)(b0 + b) * p.T + t) * p.a_dim + p.cols[m - 1]) : 0.f;
+    if (m > 0) v = (b0 + b < p.B) ? __ldg(p.A + ((size_t)(b0 + b) * p.T + t) * p.a_dim + active_col(p, m - 1)) : 0.f;
     sc[idx] = v;
   }
 }
@@ -256,7 +256,7 @@ __global__ void __launch_bounds__(FT) bwd_fp32_kernel(DevProblem p, const float*
       for (int b = 0; b < BT; ++b) acc[b] = live ? fmaf(p.J0, stats[b * 4], (1.f - p.alpha) * gs[j * BT + b]) : 0.f;
       // m = 0 is Wo, m >= 1 are the active Wa matrices, all in their original [i][j] layout
       for (int m = 0; m < p.n_mat; ++m) {
-        const float* W = (m == 0) ? p.Wo : p.Wa + (size_t)p.cols[m - 1] * N * N;
+        const float* W = (m == 0) ? p.Wo : p.Wa + (size_t)active_col(p, m - 1) * N * N;
         float tmp[BT];
 #pragma unroll
         for (int b = 0; b < BT; ++b) tmp[b] = 0.f;
@@ -299,7 +299,7 @@ __global__ void __launch_bounds__(FT) bwd_fp32_kernel(DevProblem p, const float*
         const int m = 1 + idx / BT, b = idx % BT;
         float v = 0.f;
         for (int w = 0; w < FT / 32; ++w) v += dacc[(m * BT + b) * (FT / 32) + w];
-        if (b0 + b < p.B) in.grad_A[((size_t)(b0 + b) * p.T + t) * p.a_dim + p.cols[m - 1]] = v;
+        if (b0 + b < p.B) in.grad_A[((size_t)(b0 + b) * p.T + t) * p.a_dim + active_col(p, m - 1)] = v;
       }
       __syncthreads();  // dacc is zeroed at the top of the next step
     }
@@ -341,7 +341,7 @@ __global__ void __launch_bounds__(256) dw_fp32_kernel(DevProblem p, const float*
     float dv[4] = {0.f, 0.f, 0.f, 0.f}, rv[4] = {0.f, 0.f, 0.f, 0.f};
     if (k < k_end) {
       const int t = (int)(k / p.B), b = (int)(k % p.B);
-      const float sc = (m == 0) ? 1.f : __ldg(p.A + ((size_t)b * p.T + t) * p.a_dim + p.cols[m - 1]);
+      const float sc = (m == 0) ? 1.f : __ldg(p.A + ((size_t)b * p.T + t) * p.a_dim + active_col(p, m - 1));
       const float* drow = delta + (size_t)k * N;
       const float* rrow = (t == 0) ? p.r_init + (size_t)b * N : hist + ((size_t)(t - 1) * p.B + b) * N;
 #pragma unroll
@@ -397,7 +397,7 @@ __global__ void dw_reduce_kernel(DevProblem p, const float* __restrict__ partial
       grad_Wo[e] = p.J1 * acc;
       if (raw != nullptr) raw[e] = acc;
     } else {
-      grad_Wa[(size_t)p.cols[m - 1] * NN + e] = acc;
+      grad_Wa[(size_t)active_col(p, m - 1) * NN + e] = acc;
     }
   }
 }

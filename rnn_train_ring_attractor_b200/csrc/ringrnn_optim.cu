@@ -4,6 +4,8 @@
 // Same arithmetic as those two calls (L2 norm over all gradients, coefficient max_norm / (norm + 1e-6) clamped to 1;
 // Adam without weight decay or amsgrad, bias-corrected).  The norm is summed in double precision in a fixed order:
 // bit-reproducible.
+#include <math.h>
+
 #include "ringrnn_common.cuh"
 
 namespace ringrnn {
@@ -31,7 +33,7 @@ __global__ void grad_sq_partial_kernel(const float* __restrict__ g, size_t n, do
 
 __global__ void clip_adam_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
                                  float* __restrict__ v, size_t n, float lr, float beta1, float beta2, float eps,
-                                 float bias1, float bias2_sqrt, float max_norm, double* __restrict__ scratch) {
+                                 float step_size, float bias2_sqrt, float max_norm, double* __restrict__ scratch) {
   __shared__ float coef_s;
   if (threadIdx.x == 0) {
     double tot = 0.0;
@@ -47,7 +49,6 @@ __global__ void clip_adam_kernel(float* __restrict__ p, const float* __restrict_
   }
   __syncthreads();
   const float coef = coef_s;
-  const float step_size = lr / bias1;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const float gi = g[i] * coef;
     const float mi = beta1 * m[i] + (1.f - beta1) * gi;
@@ -74,11 +75,13 @@ extern "C" int ringrnn_clip_adam(float* params, const float* grads, float* exp_a
     grad_sq_partial_kernel<<<NORM_BLOCKS, 256, 0, s>>>(grads, n, scratch);
   }
   RINGRNN_CUDA_TRY(cudaGetLastError());
-  const float bias1 = 1.f - powf(beta1, (float)step);
-  const float bias2_sqrt = sqrtf(1.f - powf(beta2, (float)step));
+  // bias corrections in double on the host and rounded once, as torch.optim.Adam computes them (Python floats)
+  const double bias1 = 1.0 - pow((double)beta1, (double)step);
+  const float step_size = (float)((double)lr / bias1);
+  const float bias2_sqrt = (float)sqrt(1.0 - pow((double)beta2, (double)step));
   {
     LaunchScope ls(K_REDUCE, s);
-    clip_adam_kernel<<<296, 256, 0, s>>>(params, grads, exp_avg, exp_avg_sq, n, lr, beta1, beta2, eps, bias1, bias2_sqrt,
+    clip_adam_kernel<<<296, 256, 0, s>>>(params, grads, exp_avg, exp_avg_sq, n, lr, beta1, beta2, eps, step_size, bias2_sqrt,
                                         max_norm, scratch);
   }
   RINGRNN_CUDA_TRY(cudaGetLastError());

@@ -86,6 +86,7 @@ __device__ __forceinline__ bool mbar_try_wait_cluster_acquire(uint32_t bar, uint
 struct WaitCtx {
   volatile int* dead;  // shared memory flag of this CTA
   int* status;         // global status word (may be nullptr)
+  long long limit = WAIT_LIMIT_CYCLES;  // cycles after which a wait is abandoned
 };
 
 // Waits for the phase with the given parity.  Returns false if the wait was abandoned.
@@ -106,7 +107,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
         *w.dead = 1;
         return false;
       }
-      if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+      if (clock64() - t0 > w.limit) {
         *w.dead = 1;
         if (w.status != nullptr) atomicCAS(w.status, 0, code);
         return false;

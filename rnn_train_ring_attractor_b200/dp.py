@@ -6,8 +6,44 @@ The reference is single-process; samples never interact in the recurrence and on
 whole multi-GPU story.  Works on any torch.distributed backend (NCCL on GPUs; gloo in the CPU tests, which
 exercise the sharding and buffer logic with a stand-in for the kernel call).
 """
+import datetime
+
 import torch
 import torch.distributed as dist
+
+
+class PeerLostError(RuntimeError):
+    """A rank of the data-parallel group left, or did not reach the gradient exchange in time."""
+
+
+def init_process_group(backend, timeout_s=600.0, **kw):
+    """torch.distributed.init_process_group with a finite collective timeout: a gradient all-reduce that a peer never
+    joins ends with an error after `timeout_s` instead of waiting for ever (the reference is single-process and has no
+    counterpart; its only failure mode is std::exit, cpp/cuda_common.cuh:30-39)."""
+    return dist.init_process_group(backend, timeout=datetime.timedelta(seconds=float(timeout_s)), **kw)
+
+
+class PeerMonitor:
+    """Host-side notice board on the process group's key-value store: a rank that leaves between steps says so, and the
+    others find out BEFORE they launch the next step -- with no kernel or collective in flight on anybody's GPU.
+
+        mon = PeerMonitor(rank, world)          # after init_process_group
+        mon.check()                             # before every step: raises PeerLostError if somebody left
+        mon.leave("out of data")                # on the way out, between steps
+    """
+
+    def __init__(self, rank, world, store=None, prefix="ringrnn/left/"):
+        self.rank, self.world, self.prefix = rank, world, prefix
+        self.store = store if store is not None else dist.distributed_c10d._get_default_store()
+
+    def leave(self, reason=""):
+        self.store.set(f"{self.prefix}{self.rank}", reason or "left")
+
+    def check(self):
+        for r in range(self.world):
+            if r != self.rank and self.store.check([f"{self.prefix}{r}"]):
+                why = self.store.get(f"{self.prefix}{r}").decode(errors="replace")
+                raise PeerLostError(f"rank {r} left the data-parallel group ({why}); not launching the next step")
 
 
 def shard_rows(t, rank, world):
@@ -30,14 +66,26 @@ def split_grad_buffer(buf, N, a_dim):
             "dJ": buf[(1 + a_dim) * nn:(1 + a_dim) * nn + 2], "loss_parts": buf[(1 + a_dim) * nn + 2:]}
 
 
-def allreduce_grad_buffer(buf, group=None):
-    """Sum over ranks, in place.  No-op without an initialised process group or with one rank."""
+def allreduce_grad_buffer(buf, group=None, timeout_s=None):
+    """Sum over ranks, in place.  No-op without an initialised process group or with one rank.
+
+    A peer that never arrives ends the call with PeerLostError: after `timeout_s` where the backend can wait with a
+    limit on the host (gloo), else after the process group's own timeout (see init_process_group).  The buffer's
+    contents are then undefined and the group should be torn down."""
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
+        try:
+            if timeout_s is not None and dist.get_backend(group) == "gloo":
+                work = dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group, async_op=True)
+                work.wait(datetime.timedelta(seconds=float(timeout_s)))
+            else:
+                dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
+        except RuntimeError as e:  # torch raises DistBackendError / RuntimeError on a timed-out or aborted collective
+            raise PeerLostError(f"gradient all-reduce did not complete: {e}") from e
     return buf
 
 
-def train_step(step_fn, local_inputs, N, a_dim, global_batch, T, buf=None, group=None, bump_weight=0.2):
+def train_step(step_fn, local_inputs, N, a_dim, global_batch, T, buf=None, group=None, bump_weight=0.2,
+               timeout_s=None):
     """Run one data-parallel fwd + loss + bwd.
 
     `step_fn(local_inputs, inv_count, grad_buffer) -> loss_parts[2]` runs the local shard and leaves
@@ -50,7 +98,7 @@ def train_step(step_fn, local_inputs, N, a_dim, global_batch, T, buf=None, group
         buf = torch.empty(grad_buffer_numel(N, a_dim), dtype=torch.float32, device=device)
     parts = step_fn(local_inputs, 1.0 / (global_batch * T), buf)
     buf[-2:].copy_(parts)
-    allreduce_grad_buffer(buf, group)
+    allreduce_grad_buffer(buf, group, timeout_s)
     out = split_grad_buffer(buf, N, a_dim)
     loss = out["loss_parts"][0] + bump_weight * out["loss_parts"][1]
     return loss, out

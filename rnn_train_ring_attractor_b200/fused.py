@@ -15,7 +15,7 @@ import torch
 from torch.autograd import Function
 
 from . import _lib
-from .ring_rnn_cuda import _check_tensor, _scalar, _scratch, active_columns, choose_precision
+from .ring_rnn_cuda import _check_tensor, _scalar, _scratch, active_columns, choose_precision, nvtx_range
 
 _decode_cache = {}
 
@@ -57,7 +57,7 @@ class RingRnnFusedFunc(Function):
             inv_count = 1.0 / (B * T)
         u, v = decode_vectors(N, dev)
         L = _lib.lib()
-        with torch.cuda.device(dev):
+        with torch.cuda.device(dev), nvtx_range("ringrnn_fused_fwd"):
             stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
             p = _lib.make_problem(B, T, N, a_dim, act, prec, _scalar(J0), _scalar(J1), alpha,
                                   action_signal.data_ptr(), Wa.data_ptr(), Wo.data_ptr(), r_init.data_ptr(), active,
@@ -101,7 +101,7 @@ class RingRnnFusedFunc(Function):
         want_r = ctx.needs_input_grad[5]
         want_a = ctx.needs_input_grad[0]
         L = _lib.lib()
-        with torch.cuda.device(dev):
+        with torch.cuda.device(dev), nvtx_range("ringrnn_fused_bwd"):
             p = _lib.make_problem(B, T, N, a_dim, ctx.act, ctx.prec, _scalar(ctx.J0), _scalar(ctx.J1), ctx.alpha,
                                   action_signal.data_ptr(), Wa.data_ptr(), Wo.data_ptr(), r_init.data_ptr(),
                                   ctx.active, ckpt_every=ctx.ckpt_every)
@@ -176,7 +176,7 @@ def ring_rnn_rollout(action_signal, Wa, J0, J1, Wo, r_init, alpha, activation, p
     prec = choose_precision(B, T, N, a_dim, act, len(active), precision)
     u, v = decode_vectors(N, dev)
     L = _lib.lib()
-    with torch.cuda.device(dev), torch.no_grad():
+    with torch.cuda.device(dev), torch.no_grad(), nvtx_range("ringrnn_rollout"):
         p = _lib.make_problem(B, T, N, a_dim, act, prec, _scalar(J0), _scalar(J1), alpha, action_signal.data_ptr(),
                               Wa.data_ptr(), Wo.data_ptr(), r_init.data_ptr(), active)
         xy = torch.empty(2, B, T, device=dev, dtype=torch.float32)

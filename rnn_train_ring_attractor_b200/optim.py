@@ -4,7 +4,8 @@ The reference training loop (train_general_ring_no_gain.py:331-344) calls, per s
 ``torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)`` and ``torch.optim.Adam.step()`` on four separate
 parameter tensors and reads the loss back with ``.item()``.  Here the parameters live in ONE contiguous fp32 buffer with
 the layout of the data-parallel gradient buffer (``[Wo | Wa | J0 J1]``, dp.py), so the all-reduced gradient can be
-applied by a single fused kernel (``ringrnn_clip_adam``) without any host synchronisation.
+applied by a single fused kernel (``ringrnn_clip_adam``) without any host synchronisation.  As in the reference, only
+Wo and Wa are trained unless asked otherwise; J0 and J1 ride along in the buffer as constants.
 """
 import ctypes as C
 
@@ -43,13 +44,19 @@ class FlatRingParams:
 class FusedClipAdam:
     """clip_grad_norm_(max_norm) + Adam(lr, betas, eps) on a flat parameter buffer, one library call per step.
 
-    Defaults follow the reference (Adam lr 1e-3, clip 1.0: train_general_ring_no_gain.py:312, :335).
+    Defaults follow the reference (Adam lr 1e-3, clip 1.0: train_general_ring_no_gain.py:312, :335).  In the reference
+    J0 and J1 are plain floats (train_general_ring_no_gain.py:47-48): model.parameters() is {Wo, Wa}, so neither the
+    clip norm nor the update sees them.  The same holds here by default: when the buffer has the [Wo | Wa | J0 J1]
+    layout (`n_fixed_tail` = 2 trailing elements), the norm and the update cover Wo and Wa only and J0, J1 keep their
+    values.  `train_J=True` opts into training them as well (their gradients then enter the clip norm).
     """
 
-    def __init__(self, flat_params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, max_norm=1.0):
+    def __init__(self, flat_params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, max_norm=1.0, train_J=False, n_fixed_tail=2):
         if flat_params.dtype != torch.float32 or not flat_params.is_cuda or not flat_params.is_contiguous():
             raise ValueError("flat_params must be a contiguous fp32 CUDA tensor")
         self.params = flat_params
+        self.train_J = bool(train_J)
+        self.n_updated = flat_params.numel() - (0 if train_J else int(n_fixed_tail))
         self.lr, self.betas, self.eps, self.max_norm = lr, betas, eps, max_norm
         self.exp_avg = torch.zeros_like(flat_params)
         self.exp_avg_sq = torch.zeros_like(flat_params)
@@ -57,7 +64,8 @@ class FusedClipAdam:
         self._scratch = torch.zeros(129, dtype=torch.float64, device=flat_params.device)
 
     def step(self, flat_grads):
-        """Applies one update; returns a 0-dim device tensor holding the unclipped gradient norm (no sync)."""
+        """Applies one update; returns a 0-dim device tensor holding the unclipped gradient norm of the updated
+        elements (no sync)."""
         if flat_grads.shape != self.params.shape or flat_grads.dtype != torch.float32 or not flat_grads.is_contiguous():
             raise ValueError("flat_grads must match the parameter buffer (contiguous fp32)")
         self.step_count += 1
@@ -65,7 +73,7 @@ class FusedClipAdam:
             stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
             _lib.check(_lib.lib().ringrnn_clip_adam(
                 self.params.data_ptr(), flat_grads.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
-                self.params.numel(), self.lr, self.betas[0], self.betas[1], self.eps, self.step_count, self.max_norm,
+                self.n_updated, self.lr, self.betas[0], self.betas[1], self.eps, self.step_count, self.max_norm,
                 self._scratch.data_ptr(), stream))
         return self._scratch[128]
 

@@ -16,13 +16,32 @@ Arithmetic mode: `set_precision("bf16" | "fp32" | "auto")` or the RINGRNN_PRECIS
 "auto" takes the bf16 tensor-core path whenever it supports the shape, else the fp32 path, which is the
 reference's own dispatch rule in spirit (cpp/fwd.cu:36).
 """
+import contextlib
 import ctypes as C
 import os
+import weakref
 
 import torch
 from torch.autograd import Function
 
 from . import _lib
+
+
+@contextlib.contextmanager
+def nvtx_range(name):
+    """NVTX range around a library call (the reference brackets its fwd/bwd the same way for its profiles,
+    legacy/bwd_fp32.py:705-740); a no-op when torch has no CUDA runtime to push to."""
+    pushed = False
+    try:
+        torch.cuda.nvtx.range_push(name)
+        pushed = True
+    except Exception:
+        pass
+    try:
+        yield
+    finally:
+        if pushed:
+            torch.cuda.nvtx.range_pop()
 
 _precision = os.environ.get("RINGRNN_PRECISION", "auto")
 
@@ -56,15 +75,35 @@ def _check_tensor(name, t):
         raise RuntimeError(f"{name} must be contiguous")  # TORCH_CHECK of cpp/fwd.cpp:31-35
 
 
+_active_cache = {}  # id(tensor) -> (weakref, _version, columns)
+
+
 def active_columns(action_signal):
     """Columns of A that are not identically zero.  The root training script pads [L, R] to 16 columns
     with zeros (train_general_ring_no_gain.py:200-223); their matrices cannot influence the result and
-    their gradients are exactly zero, so both directions skip them.  One small device->host read."""
+    their gradients are exactly zero, so both directions skip them.
+
+    Finding them costs one small device->host read (a synchronisation), so the answer is remembered per tensor
+    OBJECT and version counter: a signal that is passed again unchanged (evaluation loops, benchmarks) is not read
+    twice, while a new tensor -- even one that reuses the freed memory of an old one -- or an in-place update is.
+    More than MAX_ACTIVE non-zero columns: all columns are reported (only "all" can be expressed beyond the list)."""
     a_dim = action_signal.shape[2]
     if a_dim <= 2:
         return list(range(a_dim))
+    key = id(action_signal)
+    hit = _active_cache.get(key)
+    if hit is not None and hit[0]() is action_signal and hit[1] == action_signal._version:
+        return hit[2]
     flags = (action_signal != 0).flatten(0, 1).any(dim=0)
-    return torch.nonzero(flags).flatten().tolist()
+    cols = torch.nonzero(flags).flatten().tolist()
+    if len(cols) > _lib.MAX_ACTIVE:
+        cols = list(range(a_dim))
+    try:
+        ref = weakref.ref(action_signal, lambda _r, k=key: _active_cache.pop(k, None))
+        _active_cache[key] = (ref, action_signal._version, cols)
+    except TypeError:
+        pass
+    return cols
 
 
 def choose_precision(B, T, N, a_dim, act_code, n_active, requested=None):
@@ -72,12 +111,14 @@ def choose_precision(B, T, N, a_dim, act_code, n_active, requested=None):
     mode = requested or _precision
     if mode == "fp32":
         return _lib.PREC["fp32"]
-    p = _lib.Problem()
-    p.B, p.T, p.N, p.a_dim, p.activation, p.precision = B, T, N, a_dim, act_code, _lib.PREC["bf16"]
-    p.n_active = n_active
-    for k in range(max(n_active, 0)):
-        p.active_cols[k] = k
-    ok = _lib.lib().ringrnn_workspace_bytes(C.byref(p), _lib.WS_FWD, 1) != C.c_size_t(-1).value
+    ok = n_active <= _lib.MAX_ACTIVE  # the tensor-core kernels take at most that many active columns
+    if ok:
+        p = _lib.Problem()
+        p.B, p.T, p.N, p.a_dim, p.activation, p.precision = B, T, N, a_dim, act_code, _lib.PREC["bf16"]
+        p.n_active = n_active
+        for k in range(max(n_active, 0)):
+            p.active_cols[k] = k
+        ok = _lib.lib().ringrnn_workspace_bytes(C.byref(p), _lib.WS_FWD, 1) != C.c_size_t(-1).value
     if ok:
         return _lib.PREC["bf16"]
     if mode == "bf16":
@@ -127,7 +168,7 @@ class RingRnnCudaFunc(Function):
         active = list(range(a_dim)) if ctx.needs_input_grad[0] else active_columns(action_signal)
         prec = choose_precision(batch_size, seq_len, N, a_dim, act, len(active))
         L = _lib.lib()
-        with torch.cuda.device(dev):
+        with torch.cuda.device(dev), nvtx_range("ringrnn_fwd"):
             p = _lib.make_problem(batch_size, seq_len, N, a_dim, act, prec, _scalar(J0), _scalar(J1), alpha,
                                   action_signal.data_ptr(), Wa.data_ptr(), Wo.data_ptr(), r_init.data_ptr(), active)
             bump_history = torch.empty(seq_len, batch_size, N, device=dev, dtype=action_signal.dtype)
@@ -162,7 +203,7 @@ class RingRnnCudaFunc(Function):
         want_r = ctx.needs_input_grad[5]
         want_a = ctx.needs_input_grad[0]
         L = _lib.lib()
-        with torch.cuda.device(dev):
+        with torch.cuda.device(dev), nvtx_range("ringrnn_bwd"):
             p = _lib.make_problem(batch_size, seq_len, N, a_dim, act, ctx.prec, _scalar(ctx.J0), _scalar(ctx.J1),
                                   ctx.alpha, action_signal.data_ptr(), Wa.data_ptr(), Wo.data_ptr(),
                                   r_init.data_ptr(), ctx.active)

@@ -24,3 +24,27 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+# Achieved parity errors, printed after the run (also with -q) so that a log of the GPU suite shows how far inside
+# its stated tolerance every comparison landed.
+_ACHIEVED = []
+
+
+def report_achieved(case, **values):
+    """Record named achieved errors of one parity comparison: report_achieved("c2 bf16", hist=1.2e-3, loss=4e-6)."""
+    _ACHIEVED.append((case, values))
+
+
+@pytest.fixture
+def achieved():
+    return report_achieved
+
+
+def pytest_terminal_summary(terminalreporter):
+    if not _ACHIEVED:
+        return
+    terminalreporter.section("achieved parity errors (rel = |x-ref|_F/|ref|_F unless named otherwise)")
+    for case, values in _ACHIEVED:
+        terminalreporter.write_line(case + ": " + "  ".join(
+            f"{k}={v:.2e}" if isinstance(v, float) else f"{k}={v}" for k, v in values.items()))

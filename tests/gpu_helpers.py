@@ -28,19 +28,19 @@ def poisoned_bytes(nbytes, device="cuda"):
     return torch.full((max(int(nbytes), 16),), 255, dtype=torch.uint8, device=device)
 
 
-def problem(A, Wa, Wo, r_init, J0, J1, alpha, act, prec, active=None):
+def problem(A, Wa, Wo, r_init, J0, J1, alpha, act, prec, active=None, ckpt_every=0):
     B, T, a = A.shape
     return _lib.make_problem(B, T, Wa.shape[1], a, _lib.ACT[act], _lib.PREC[prec], J0, J1, alpha, A.data_ptr(),
-                             Wa.data_ptr(), Wo.data_ptr(), r_init.data_ptr(), active)
+                             Wa.data_ptr(), Wo.data_ptr(), r_init.data_ptr(), active, ckpt_every=ckpt_every)
 
 
 def run_forward(A, Wa, Wo, r_init, J0, J1, alpha, act, prec="fp32", active=None, history=True, decode=False,
-                save=True):
+                save=True, ckpt_every=0):
     """Calls ringrnn_fwd through the C ABI.  Returns dict(hist, saved, dec(x,y,ta), final, backs)."""
     L = _lib.lib()
     B, T, a = A.shape
     N = Wa.shape[1]
-    p = problem(A, Wa, Wo, r_init, J0, J1, alpha, act, prec, active)
+    p = problem(A, Wa, Wo, r_init, J0, J1, alpha, act, prec, active, ckpt_every)
     out = {"backs": []}
     args = _lib.FwdArgs()
     args.p = p
@@ -73,12 +73,12 @@ def run_forward(A, Wa, Wo, r_init, J0, J1, alpha, act, prec="fp32", active=None,
 
 
 def run_backward(A, Wa, Wo, r_init, J0, J1, alpha, act, fwd, grad_output=None, coefs=None, prec="fp32",
-                 active=None):
+                 active=None, ckpt_every=0):
     """Calls ringrnn_bwd through the C ABI.  `fwd` is run_forward's result.  Returns dict of gradients."""
     L = _lib.lib()
     B, T, a = A.shape
     N = Wa.shape[1]
-    p = problem(A, Wa, Wo, r_init, J0, J1, alpha, act, prec, active)
+    p = problem(A, Wa, Wo, r_init, J0, J1, alpha, act, prec, active, ckpt_every)
     args = _lib.BwdArgs()
     args.p = p
     out = {"backs": []}

@@ -149,3 +149,50 @@ def test_operator_refuses_cpu_tensors_loudly():
         m.ring_rnn_cuda_func(A, Wa, -0.1, 0.1, Wo, r0, 0.1, "swish")
     with pytest.raises(RuntimeError, match="CUDA tensor"):
         m.ring_rnn_cuda_func(A, Wa, -0.1, 0.1, Wo, r0, 0.1, "tanh")
+
+
+def test_documented_binding_matches_the_real_struct():
+    """INTEGRATION.md prints the ctypes Problem structure a maintainer would paste into the reference: its field list must
+    be the one the library is built with (a short structure hands check_problem garbage)."""
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    block = text[text.index("class Problem(C.Structure)"):]
+    block = block[:block.index("def fwd(")]
+    documented = re.findall(r'\("([A-Za-z0-9_]+)",\s*C\.', block)
+    assert documented == [f[0] for f in _lib.Problem._fields_]
+    # and the header declares the same members in the same order
+    hdr = open(os.path.join(ROOT, "include", "ringrnn.h")).read()
+    body = hdr[hdr.index("typedef struct RingRnnProblem {"):hdr.index("} RingRnnProblem;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    members = re.findall(r"([A-Za-z_][A-Za-z0-9_]*)\s*(?:\[[^\]]*\])?\s*[,;]", body.split("{", 1)[1])
+    assert members == [f[0] for f in _lib.Problem._fields_], members
+
+
+def test_more_than_64_action_columns_only_in_fp32_mode(L):
+    """The reference's entry points take any a_dim (cpp/fwd.cu:21-50).  Here "all columns" (n_active < 0) with
+    a_dim > RINGRNN_MAX_ACTIVE is a valid fp32-mode problem and an unsupported bf16-mode one."""
+    p = _problem(a_dim=80, prec=0)
+    assert p.n_active == -1
+    assert L.ringrnn_workspace_bytes(C.byref(p), 0, 1) not in (0, C.c_size_t(-1).value)
+    assert L.ringrnn_workspace_bytes(C.byref(p), 2, 1) != C.c_size_t(-1).value
+    p16 = _problem(a_dim=80, prec=1)
+    assert L.ringrnn_workspace_bytes(C.byref(p16), 0, 1) == C.c_size_t(-1).value
+    a = _lib.FwdArgs()
+    a.p = p16
+    a.bump_history = 1
+    assert L.ringrnn_fwd(C.byref(a), None) == _lib.ERR_UNSUPPORTED
+    # an explicit list cannot name more than 64 columns; a longer list must be all of them
+    q = _problem(a_dim=80, prec=0, active=list(range(80)))
+    assert q.n_active == -1
+    with pytest.raises(ValueError):
+        _problem(a_dim=80, prec=0, active=list(range(70)))
+
+
+def test_device_status_surface_without_a_gpu(L):
+    """Nothing has been launched: no deferred failure to report, and reading the report is not an error."""
+    code = C.c_int(123)
+    assert L.ringrnn_device_status(C.byref(code)) == 0 and code.value == 0
+    assert L.ringrnn_device_status(None) == 0
+    assert L.ringrnn_selftest_wait(1000, 7, None, None) == 1      # no status word
+    assert L.ringrnn_selftest_wait(-1, 7, 1, None) == 1           # negative limit
+    assert L.ringrnn_selftest_wait(1000, 0, 1, None) == 1         # code 0 would be indistinguishable from success
+    _lib.raise_if_device_error()

@@ -33,12 +33,72 @@ def test_clip_adam_matches_torch(n, max_norm):
     ref_clip = max_norm if max_norm > 0 else 1e30
     ref, ref_norms = _torch_reference_steps(p0, grads, 1e-3, (0.9, 0.999), 1e-8, ref_clip)
     flat = p0.cuda()
-    opt = FusedClipAdam(flat, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, max_norm=max_norm)
+    opt = FusedClipAdam(flat, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, max_norm=max_norm, train_J=True)  # every element
     for gi, rn in zip(grads, ref_norms):
         norm = opt.step(gi.cuda())
         assert abs(float(norm) - rn) < 1e-5 * rn
     assert orc.rel_err(flat, ref) < 1e-6
     assert float((flat.cpu().double() - ref).abs().max()) < 1e-6
+    # the UPDATE itself (not hidden behind the size of the parameters): fp32 arithmetic against torch's double
+    assert orc.rel_err(flat.cpu().double() - p0.double(), ref - p0.double()) < 1e-4
+
+
+def test_clip_adam_leaves_j0_j1_alone_by_default():
+    """In the reference J0 and J1 are plain floats (train_general_ring_no_gain.py:47-48): model.parameters() is
+    {Wo, Wa}.  With the flat [Wo | Wa | J0 J1] buffer the default step must neither move the two trailing elements nor
+    count their gradients in the clip norm."""
+    from rnn_train_ring_attractor_b200.optim import FusedClipAdam
+    n = 3 * 16 * 16 + 2
+    g = torch.Generator().manual_seed(1)
+    p0 = torch.randn(n, generator=g)
+    grads = [torch.randn(n, generator=g) * s for s in (2.0, 0.1)]
+    for gr in grads:
+        gr[-2:] = 1e4  # dJ0 = sum_ij G_ij is large in practice: it must not shrink the Wo / Wa updates
+    ref, ref_norms = _torch_reference_steps(p0[:-2], [gr[:-2] for gr in grads], 1e-3, (0.9, 0.999), 1e-8, 1.0)
+    flat = p0.cuda()
+    opt = FusedClipAdam(flat)
+    for gi, rn in zip(grads, ref_norms):
+        assert abs(float(opt.step(gi.cuda())) - rn) < 1e-5 * rn
+    assert torch.equal(flat[-2:].cpu(), p0[-2:])
+    assert orc.rel_err(flat[:-2].cpu().double() - p0[:-2].double(), ref - p0[:-2].double()) < 1e-4
+
+
+def test_training_steps_follow_the_reference_loop():
+    """K steps of fused forward + loss + backward (dp.train_step) + FusedClipAdam against the oracle's reference-shaped
+    loop: autograd, clip_grad_norm_(1.0) and torch.optim.Adam on {Wo, Wa}, J0 / J1 fixed
+    (train_general_ring_no_gain.py:312-336)."""
+    from rnn_train_ring_attractor_b200 import dp
+    from rnn_train_ring_attractor_b200.optim import FlatRingParams, FusedClipAdam
+    N, B, T, K = 48, 24, 20, 4
+    case = orc.make_case(N, B, T, "tanh", seed=2)
+    Wo = case.Wo.clone().requires_grad_(True)
+    Wa = case.Wa.clone().requires_grad_(True)
+    opt_ref = torch.optim.Adam([Wo, Wa], lr=1e-3)
+    ref_losses = []
+    for _ in range(K):
+        hist = orc.ring_forward_ref(case.A, Wa, case.J0, case.J1, Wo, case.r_init, case.alpha, case.act)
+        loss = orc.training_loss_ref(hist, case.target)
+        opt_ref.zero_grad()
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_([Wo, Wa], 1.0)
+        opt_ref.step()
+        ref_losses.append(float(loss))
+    params = FlatRingParams(case.Wo.cuda(), case.Wa.cuda(), case.J0, case.J1)
+    opt = FusedClipAdam(params.flat)
+    ins = tuple(t.cuda() for t in (case.A, case.r_init, case.target))
+    buf = torch.empty(dp.grad_buffer_numel(N, 2), dtype=torch.float32, device="cuda")
+    losses = []
+    for _ in range(K):
+        fn = dp.fused_step_fn(params.Wa, case.J0, case.J1, params.Wo, case.alpha, case.act, precision="fp32")
+        loss, _ = dp.train_step(fn, ins, N, 2, B, T, buf=buf)
+        opt.step(buf[:params.flat.numel()])
+        losses.append(float(loss))
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 1e-4 * max(1.0, abs(b)), (losses, ref_losses)
+    assert orc.rel_err(params.Wo, Wo) < 1e-5 and orc.rel_err(params.Wa, Wa) < 1e-5
+    # the update, not just the weights: K steps of lr 1e-3 move every weight by up to K * 1e-3
+    assert orc.rel_err(params.Wo.cpu() - case.Wo, Wo.detach() - case.Wo) < 1e-3
+    assert abs(float(params.J[0]) - case.J0) < 1e-7 and abs(float(params.J[1]) - case.J1) < 1e-7
 
 
 def test_flat_params_views_and_state_roundtrip(tmp_path):

@@ -61,6 +61,35 @@ def test_static_scratch_matches_caller_scratch_on_consecutive_calls():
             assert _close(g, w)
 
 
+def test_static_scratch_at_its_capacity_and_without_allocating():
+    """B == RINGRNN_STATIC_LOSS_MAX_B exactly (the last valid entries of the built-in array), compared with caller
+    scratch; and the reason the entry point exists: with its outputs in place, a call takes no device memory -- neither
+    from the driver (free bytes unchanged) nor from torch's pool."""
+    L = _lib.lib()
+    B, T = _lib.STATIC_LOSS_MAX_B, 2
+    ins = _inputs(B, T, 3)
+    want = _call(False, B, T, ins, float("nan"))
+    got = _call(True, B, T, ins, None)  # also the first-call set-up, if this test runs alone
+    for g, w in zip(got, want):
+        assert torch.isfinite(g).all() and _close(g, w)
+    # second call with preallocated outputs: nothing may be allocated
+    x, y, ta, target = ins
+    outs = [torch.empty(B, T, device="cuda") for _ in range(4)]
+    parts = torch.empty(2, device="cuda")
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    alloc0, reserved0 = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    rc = L.ringrnn_angle_loss_static(B, T, x.data_ptr(), y.data_ptr(), ta.data_ptr(), target.data_ptr(), 0.2,
+                                     1.0 / (B * T), *[o.data_ptr() for o in outs], parts.data_ptr(), None)
+    torch.cuda.synchronize()
+    assert rc == 0
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, "the call changed the device's free memory"
+    assert torch.cuda.memory_allocated() == alloc0 and torch.cuda.memory_reserved() == reserved0
+    for g, w in zip(outs + [parts], want):
+        assert _close(g, w)
+
+
 def test_static_scratch_rejects_oversize_and_bad_arguments():
     L = _lib.lib()
     too_big = _lib.STATIC_LOSS_MAX_B + 1
