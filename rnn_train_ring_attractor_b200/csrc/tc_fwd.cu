@@ -25,6 +25,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmR0, const TcFwdParams p) {
   using C_ = Cfg<NP, PAIR>;
   static_assert(!GEN || (C_::ROUNDS == 1 && !PAIR), "weight groups: one K round, single CTAs");
+  constexpr bool EARLY = C_::EARLY && !GEN;  // chunk 0 of a step is published while sub-slice 1 is still being worked on
   extern __shared__ uint8_t smem_raw[];
   const Ctx<NP, PAIR> c = setup_cta<NP, PAIR>(smem_raw, p.dec_u, p.dec_v, p.N, p.status);
   const int ng = GEN ? p.ng : 1;
@@ -55,7 +56,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           tma_load_2d(a_base + slot * CHUNK_BYTES, &tmR0, bars + OFF_A_FULL + 8 * slot, (round * C_::SLOTS + slot) * 64,
                       tile * C_::TILE_ROWS + c.half * 128);
         }
-      });
+      }, EARLY);
     }
   } else {
     reg_inc<HIGH_REGS>();
@@ -74,6 +75,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     const int rq = (2 * q) / C_::SLOTS;  // the K round this CTA's own chunks belong to
     FreePhases<NP, PAIR> freed;
     uint32_t g = 0;
+    uint32_t n_sent = 0, sent_waited = 0;  // early publication: copies of own chunk 0 sent / known to have arrived
     bool stop = false;  // a wait of this CTA was abandoned (the status word says which): same value in all 256 threads
     for (int tile = cluster_id; tile < p.n_tiles && !stop; tile += n_clusters) {
       const int b = tile * C_::TILE_ROWS + c.half * 128 + row;
@@ -130,6 +132,19 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               tmem_ld_wait();
             }
             release_accumulator<NP, PAIR>(c, s, lane);  // the accumulator is in registers: hand it back
+            if constexpr (EARLY) {
+              if (s == 1 && t + 1 < T) {
+                // Every CTA's MMAs of this step are complete (this CTA's: accumulator 1 is; the others': the "free"
+                // phase), so the peers' slots may be overwritten: send chunk 0, which all threads wrote into this CTA's
+                // own slot while sub-slice 1 was still being multiplied.  Its transfer now overlaps the arithmetic of
+                // sub-slice 1 below instead of standing between two steps.
+                freed.before_publish(c, g + 1, rq, 208);
+                if (send_chunk<NP, PAIR>(c, 0, warp, lane, 3, p.Rh != nullptr ? &tmR0 : nullptr, q * 128,
+                                         (t + 1) * p.BP + tile * C_::TILE_ROWS + c.half * 128))
+                  stop = true;
+                ++n_sent;
+              }
+            }
           } else {
             for (int grp = 0; grp < ng; ++grp) {
               // coefficients of the group's three matrices: J1 for Wo, the action scalar for an action matrix
@@ -252,7 +267,22 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             sg[0] = zero;
             sg[p.BP] = __brev(negr);
           }
+          if constexpr (EARLY) {
+            if (s == 0) {
+              // this CTA's MMAs no longer read the slot of its own chunk 0 (one phase per step, consumed every step)
+              mbar_wait(bars + OFF_OWN0_FREE, g & 1u, wctx, 209);
+              if (t + 1 < T) {
+                // ... and every copy sent out of that slot so far has arrived at its peer
+                while (sent_waited < n_sent) {
+                  mbar_wait<true>(bars + OFF_SENT_DONE, sent_waited & 1u, wctx, 209);
+                  ++sent_waited;
+                }
+                write_chunk<NP, PAIR>(c, packed, 0, row, h);
+              }
+            }
+          }
         }
+        if (stop) break;
         // every CTA of the cluster has finished reading what the slots of this CTA's chunks held (every phase of
         // the barriers is waited for, published or not, so that none is skipped); then publish r_t:
         // it becomes the A operand of step t+1 everywhere and, in training, row block t+1 of the saved state
@@ -260,8 +290,20 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (t + 1 < T) {
           freed.before_publish(c, g + 1, rq, 208);
           if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 10);
-          stop = publish_chunks<NP, PAIR>(c, packed, row, h, warp, lane, p.Rh != nullptr ? &tmR0 : nullptr, q * 128,
-                                          (t + 1) * p.BP + tile * C_::TILE_ROWS + c.half * 128);
+          if constexpr (EARLY) {
+            // chunk 1: the TMA stores issued so far have finished reading the slots (the issuing thread waits before
+            // it arrives), then write, then send
+            if (p.Rh != nullptr) {
+              if (warp == 4 && lane == 0) bulk_wait_read<0>();
+              named_bar_sync(2, 256);
+            }
+            write_chunk<NP, PAIR>(c, packed + 16, 1, row, h);
+            stop = send_chunk<NP, PAIR>(c, 1, warp, lane, 1, p.Rh != nullptr ? &tmR0 : nullptr, q * 128,
+                                        (t + 1) * p.BP + tile * C_::TILE_ROWS + c.half * 128);
+          } else {
+            stop = publish_chunks<NP, PAIR>(c, packed, row, h, warp, lane, p.Rh != nullptr ? &tmR0 : nullptr, q * 128,
+                                            (t + 1) * p.BP + tile * C_::TILE_ROWS + c.half * 128);
+          }
           if (stop) break;
         } else {
           freed.end_of_step(c, g, 208);

@@ -151,6 +151,10 @@ struct Cfg {
   static constexpr bool RESIDENT = NS_FIT >= TILES;
   static constexpr int NS = RESIDENT ? TILES : (NS_FIT > 16 ? 16 : NS_FIT);
   static constexpr int SMEM = 1024 + A_BYTES + NS * WT_BYTES + AUX + STAGE_BYTES;
+  // Early publication (forward, single CTAs, one K round, more than one slice): a CTA sends the new chunk of its
+  // sub-slice 0 to its peers while it still works on sub-slice 1, so that half of the state exchange is hidden behind
+  // the second half of the epilogue instead of standing between two steps.
+  static constexpr bool EARLY = !PAIR && ROUNDS == 1 && C > 1;
   static_assert(NS >= 2, "weight ring too small");
   static_assert(NS <= 16, "barrier block sized for 16 stages");
   static_assert(WT_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
@@ -171,6 +175,8 @@ constexpr uint32_t OFF_TMEM_SLOT = 376;
 constexpr uint32_t OFF_DEAD = 380;
 constexpr uint32_t OFF_A_PAIR = 384;   // [8]  (even CTA of a pair) chunk kc is complete in the odd CTA too
 constexpr uint32_t OFF_STORE_DONE = 448;  // (two rounds) the TMA store of this CTA's own chunks has read them
+constexpr uint32_t OFF_OWN0_FREE = 456;   // (early publication) this CTA's MMAs no longer read the slot of its own chunk 0
+constexpr uint32_t OFF_SENT_DONE = 464;   // (early publication) the peers have received the copies of own chunk 0
 constexpr uint32_t OFF_UV = 512;       // float u[128], v[128]
 
 template <int REGS>
@@ -389,6 +395,8 @@ __device__ __forceinline__ Ctx<NP, PAIR> setup_cta(uint8_t* smem_raw, const floa
     mbar_init(c.bars + OFF_ALL_FREE, C_::C);
     mbar_init(c.bars + OFF_ALL_FREE + 8, C_::C);
     mbar_init(c.bars + OFF_STORE_DONE, 1);
+    mbar_init(c.bars + OFF_OWN0_FREE, 1);
+    mbar_init(c.bars + OFF_SENT_DONE, C_::C > 1 ? C_::C - 1 : 1);
     fence_mbar_init();
   }
   if (threadIdx.x < 256) {
@@ -486,6 +494,7 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
   using namespace tc;
   constexpr int KC = C_::KC, NS = C_::NS, SL = C_::SLOTS, R = C_::ROUNDS;
   constexpr uint32_t idesc = make_idesc_bf16(PAIR ? 256 : 128, C_::RB, 0, 0);
+  constexpr bool EARLY_FWD = FWD && !GEN && C_::EARLY;
   const int rot = (2 * c.q) % SL, rq = (2 * c.q) / SL;
   uint32_t ph = 0, npub = 0;
   int wst = 0;          // ring stage of the next weight tile
@@ -575,6 +584,9 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
                 wpar ^= 1u;
               }
             }
+            // early publication: the passes start at this CTA's own chunks, so after the first tile of the last pass
+            // nothing issued later reads the slot of own chunk 0: the epilogue may overwrite it once these complete
+            if (EARLY_FWD && s == 1 && grp == ng - 1 && i == 0) commit(c.bars + OFF_OWN0_FREE);
           }
           if (round == R - 1) {
             commit(c.bars + OFF_D_FULL + 8 * acc);
@@ -610,7 +622,7 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
 // complete here" to its leader and arms its own incoming copies.
 template <int NP, bool PAIR, bool FWD, class TileStart>
 __device__ __forceinline__ void relay_loop(const Ctx<NP, PAIR>& c, uint32_t total_steps, int T, int code,
-                                           TileStart tile_start) {
+                                           TileStart tile_start, bool early_acks = false) {
   using C_ = Cfg<NP, PAIR>;
   using namespace tc;
   constexpr int KC = C_::KC, R = C_::ROUNDS;
@@ -622,6 +634,15 @@ __device__ __forceinline__ void relay_loop(const Ctx<NP, PAIR>& c, uint32_t tota
   for (uint32_t g = 0; g < total_steps; ++g) {
     for (int round = 0; round < R; ++round, ++ph) {
       if (t == 0) tile_start(it, round);
+      if (C_::EARLY && early_acks && t != 0) {
+        // early publication: chunk 0 of every peer reached this CTA as a copy out of the peer's own A slot; tell the
+        // peer once it has landed, so that the peer knows when it may overwrite that slot again
+        for (int q2 = 0; q2 < C_::C; ++q2)
+          if (q2 != c.q) {
+            if (!mbar_wait(c.bars + OFF_A_FULL + 8 * (2 * q2), ph & 1u, c.wctx, code + 2)) return;
+            mbar_arrive_cluster(c.bars + OFF_SENT_DONE, (uint32_t)q2);
+          }
+      }
       if (PAIR && !c.leader) {
         const bool next_by_copy = FWD ? (t + 1 < T) : (g + 1 < total_steps);
         for (int i = 0; i < KC; ++i) {
@@ -737,6 +758,45 @@ __device__ __forceinline__ bool publish_chunks(const Ctx<NP, PAIR>& c, const uin
         bulk_wait_read<0>();
         mbar_arrive(c.bars + OFF_STORE_DONE);
       }
+    }
+  }
+  return stop;
+}
+
+// Early publication, forward kernel (Cfg::EARLY).  The two chunks of a step are published separately:
+//   write_chunk   : every epilogue thread stores its 16 packed words of sub-slice s into the CTA's own A slot
+//   send_chunk    : after a barrier over the 256 epilogue threads, one thread marks the slot complete locally, copies
+//                   it to the peers and (training) stores it to the saved state with TMA.  Returns `stop` as
+//                   publish_chunks does.  `bar_id`: the named barrier to use (1 or 3).
+template <int NP, bool PAIR>
+__device__ __forceinline__ void write_chunk(const Ctx<NP, PAIR>& c, const uint32_t* packed16, int s, int row, int h) {
+  using C_ = Cfg<NP, PAIR>;
+  const uint32_t tile_addr = c.a_base + ((2 * c.q + s) % C_::SLOTS) * CHUNK_BYTES;
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const uint32_t unit = (uint32_t)(4 * h + v);
+    const uint32_t addr = tile_addr + row * 128 + ((unit ^ ((uint32_t)row & 7u)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed16[4 * v]), "r"(packed16[4 * v + 1]),
+                 "r"(packed16[4 * v + 2]), "r"(packed16[4 * v + 3])
+                 : "memory");
+  }
+  tc::fence_proxy_async_smem();
+}
+template <int NP, bool PAIR>
+__device__ __forceinline__ bool send_chunk(const Ctx<NP, PAIR>& c, int s, int warp, int lane, uint32_t bar_id,
+                                           const CUtensorMap* tm_store, int x0, int y) {
+  using C_ = Cfg<NP, PAIR>;
+  using namespace tc;
+  const bool stop = named_bar_or(bar_id, 256, *c.wctx.dead != 0);
+  if (warp == 4 && lane == 0 && !stop) {
+    const int slot = (2 * c.q + s) % C_::SLOTS;
+    const uint32_t tile_addr = c.a_base + slot * CHUNK_BYTES;
+    mbar_arrive(c.bars + OFF_A_FULL + 8 * slot);
+    for (int q2 = 0; q2 < C_::C; ++q2)
+      if (q2 != c.q) dsmem_bulk_copy(tile_addr, tile_addr, CHUNK_BYTES, c.bars + OFF_A_FULL + 8 * slot, c.peer_rank(q2));
+    if (tm_store != nullptr) {
+      tma_store_2d(tm_store, tile_addr, x0 + 64 * s, y);
+      bulk_commit();
     }
   }
   return stop;
