@@ -42,7 +42,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   if (warp < 4) {
     reg_dec<LOW_REGS>();
     if (warp == 0 && lane == 0) {
+#ifdef RINGRNN_NO_SPLIT
       producer_loop<NP, PAIR, GEN>(c, &tmW, total_steps, 202, ng);
+#else
+      producer_loop<NP, PAIR, GEN, EARLY>(c, &tmW, total_steps, 202, ng);
+#endif
     } else if (warp == 1 && lane == 0) {
       if (c.leader) mma_loop<NP, PAIR, true, GEN>(c, total_steps, T, 210, p.Rh != nullptr, ng);
     } else if (warp == 2 && lane == 0) {
@@ -57,6 +61,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                       tile * C_::TILE_ROWS + c.half * 128);
         }
       }, EARLY);
+    } else if (warp == 3) {
+      if constexpr (EARLY)
+        sender_loop<NP, PAIR>(c, total_steps, T, 230, p.Rh != nullptr ? &tmR0 : nullptr, p.BP, cluster_id, n_clusters);
     }
   } else {
     reg_inc<HIGH_REGS>();
@@ -132,19 +139,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               tmem_ld_wait();
             }
             release_accumulator<NP, PAIR>(c, s, lane);  // the accumulator is in registers: hand it back
-            if constexpr (EARLY) {
-              if (s == 1 && t + 1 < T) {
-                // Every CTA's MMAs of this step are complete (this CTA's: accumulator 1 is; the others': the "free"
-                // phase), so the peers' slots may be overwritten: send chunk 0, which all threads wrote into this CTA's
-                // own slot while sub-slice 1 was still being multiplied.  Its transfer now overlaps the arithmetic of
-                // sub-slice 1 below instead of standing between two steps.
-                freed.before_publish(c, g + 1, rq, 208);
-                if (send_chunk<NP, PAIR>(c, 0, warp, lane, 3, p.Rh != nullptr ? &tmR0 : nullptr, q * 128,
-                                         (t + 1) * p.BP + tile * C_::TILE_ROWS + c.half * 128))
-                  stop = true;
-                ++n_sent;
-              }
-            }
           } else {
             for (int grp = 0; grp < ng; ++grp) {
               // coefficients of the group's three matrices: J1 for Wo, the action scalar for an action matrix
@@ -272,12 +266,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               // this CTA's MMAs no longer read the slot of its own chunk 0 (one phase per step, consumed every step)
               mbar_wait(bars + OFF_OWN0_FREE, g & 1u, wctx, 209);
               if (t + 1 < T) {
-                // ... and every copy sent out of that slot so far has arrived at its peer
+                // ... every copy sent out of that slot so far has arrived at its peer, and the TMA store has read it
                 while (sent_waited < n_sent) {
                   mbar_wait<true>(bars + OFF_SENT_DONE, sent_waited & 1u, wctx, 209);
+                  mbar_wait(bars + OFF_STORE0_DONE, sent_waited & 1u, wctx, 209);
                   ++sent_waited;
                 }
                 write_chunk<NP, PAIR>(c, packed, 0, row, h);
+                named_bar_arrive(SENDER_BAR, SENDER_BAR_THREADS);  // hand it to the sender thread and carry on
+                ++n_sent;
               }
             }
           }
@@ -354,6 +351,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             if (nq + 64 * s + j < p.N) p.final_state[(size_t)b * p.N + nq + 64 * s + j] = master[s * 32 + j];
       }
     }
+    if (EARLY && stop) named_bar_arrive(SENDER_BAR, SENDER_BAR_THREADS);  // a sender waiting for the next chunk 0 is let go
     if (warp == 4 && lane == 0) bulk_wait_all<0>();  // the saved-state stores have left shared memory and landed
   }
   teardown_cta<NP, PAIR>(c);

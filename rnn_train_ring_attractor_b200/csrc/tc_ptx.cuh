@@ -130,6 +130,10 @@ __device__ __forceinline__ void tcgen05_fence_after() {
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+// arrive at a named barrier without waiting (the threads that call named_bar_sync on the same id wait for these)
+__device__ __forceinline__ void named_bar_arrive(uint32_t id, uint32_t threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 // named barrier that also returns the OR of `pred` over its participants: a decision every thread sees alike
 __device__ __forceinline__ bool named_bar_or(uint32_t id, uint32_t threads, bool pred) {
   uint32_t r;

@@ -177,6 +177,7 @@ constexpr uint32_t OFF_A_PAIR = 384;   // [8]  (even CTA of a pair) chunk kc is 
 constexpr uint32_t OFF_STORE_DONE = 448;  // (two rounds) the TMA store of this CTA's own chunks has read them
 constexpr uint32_t OFF_OWN0_FREE = 456;   // (early publication) this CTA's MMAs no longer read the slot of its own chunk 0
 constexpr uint32_t OFF_SENT_DONE = 464;   // (early publication) the peers have received the copies of own chunk 0
+constexpr uint32_t OFF_STORE0_DONE = 472; // (early publication) the TMA store of own chunk 0 has finished reading its slot
 constexpr uint32_t OFF_UV = 512;       // float u[128], v[128]
 
 template <int REGS>
@@ -397,6 +398,7 @@ __device__ __forceinline__ Ctx<NP, PAIR> setup_cta(uint8_t* smem_raw, const floa
     mbar_init(c.bars + OFF_STORE_DONE, 1);
     mbar_init(c.bars + OFF_OWN0_FREE, 1);
     mbar_init(c.bars + OFF_SENT_DONE, C_::C > 1 ? C_::C - 1 : 1);
+    mbar_init(c.bars + OFF_STORE0_DONE, 1);
     fence_mbar_init();
   }
   if (threadIdx.x < 256) {
@@ -440,7 +442,9 @@ __device__ __forceinline__ void teardown_cta(const Ctx<NP, PAIR>& c) {
 
 // Weight stream (one thread per CTA).  Tile order per step: round by round, sub-slice 0 then 1, within a sub-slice
 // the `ng` weight groups one after the other, the slots starting at this slice's own.
-template <int NP, bool PAIR, bool GEN = false>
+// SPLIT (forward with early publication): the tiles of the even slots come first, for both sub-slices, then those of
+// the odd slots -- the order in which mma_loop consumes them.
+template <int NP, bool PAIR, bool GEN = false, bool SPLIT = false>
 __device__ __forceinline__ void producer_loop(const Ctx<NP, PAIR>& c, const CUtensorMap* tmW, uint32_t total_steps,
                                               int code, int ng_arg = 1) {
   using C_ = Cfg<NP, PAIR>;
@@ -461,6 +465,21 @@ __device__ __forceinline__ void producer_loop(const Ctx<NP, PAIR>& c, const CUte
   if (C_::RESIDENT && ng == 1) {
     for (int s = 0; s < 2; ++s)
       for (int i = 0; i < KC; ++i) issue(s * KC + i, s, 0, (rot + i) % SL);
+  } else if constexpr (SPLIT) {
+    int st = 0;
+    uint32_t lap = 0;
+    for (uint32_t g = 0; g < total_steps; ++g)
+      for (int half = 0; half < 2; ++half)
+        for (int s = 0; s < 2; ++s)
+#pragma unroll 1
+          for (int i = half; i < SL; i += 2) {
+            if (lap > 0 && !mbar_wait(c.bars + OFF_W_EMPTY + 8 * st, (lap - 1) & 1u, c.wctx, code)) return;
+            issue(st, s, 0, (rot + i) % SL);
+            if (++st == NS) {
+              st = 0;
+              ++lap;
+            }
+          }
   } else {
     int st = 0;              // ring stage of the next tile
     uint32_t lap = 0;        // how many times the ring has been filled
@@ -495,6 +514,11 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
   constexpr int KC = C_::KC, NS = C_::NS, SL = C_::SLOTS, R = C_::ROUNDS;
   constexpr uint32_t idesc = make_idesc_bf16(PAIR ? 256 : 128, C_::RB, 0, 0);
   constexpr bool EARLY_FWD = FWD && !GEN && C_::EARLY;
+#ifdef RINGRNN_NO_SPLIT
+  constexpr bool SPLIT = false;
+#else
+  constexpr bool SPLIT = EARLY_FWD;
+#endif
   const int rot = (2 * c.q) % SL, rq = (2 * c.q) / SL;
   uint32_t ph = 0, npub = 0;
   int wst = 0;          // ring stage of the next weight tile
@@ -511,6 +535,67 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
 #ifdef RINGRNN_TIMELINE
     long long acc_w = 0, acc_a = 0, acc_p = 0, t0;
 #endif
+    if constexpr (SPLIT) {
+      // Split schedule (forward with early publication).  The chunks in the even slots -- chunk 0 of every slice -- are
+      // published while the epilogue of sub-slice 1 is still running, so their share of the next step's MMAs, for both
+      // accumulators, is issued first and overlaps that epilogue; the odd slots follow once chunk 1 has arrived.
+      // Accumulator s is complete after the odd half of sub-slice s.
+      const int next_t = (t + 1 == T) ? 0 : t + 1;
+      const bool next_by_copy = next_t != 0;
+      for (int half = 0; half < 2; ++half) {
+        for (int s = 0; s < 2; ++s) {
+          if (half == 0) {
+            if (g >= 1 && !mbar_wait(c.bars + OFF_D_EMPTY + 8 * s, (g - 1) & 1u, c.wctx, code + 0)) return;
+            if (s == 0) RINGRNN_STAMP(g, 0);
+          } else if (s == 0) {
+            RINGRNN_STAMP(g, 2);
+          }
+          tcgen05_fence_after();
+#pragma unroll 1
+          for (int i = half; i < SL; i += 2) {
+            const int slot = (rot + i) % SL;
+            if (s == 0) {
+#ifdef RINGRNN_TIMELINE
+              t0 = clock64();
+#endif
+              if (!mbar_wait(c.bars + OFF_A_FULL + 8 * slot, ph & 1u, c.wctx, code + 1)) return;
+#ifdef RINGRNN_TIMELINE
+              acc_a += clock64() - t0;
+              if (i == 0) RINGRNN_STAMP(g, 1);
+#endif
+              if (next_by_copy && (slot >> 1) != c.q) mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * slot, CHUNK_BYTES);
+            }
+            const int st = wst;
+#ifdef RINGRNN_TIMELINE
+            t0 = clock64();
+#endif
+            if (!mbar_wait(c.bars + OFF_W_FULL + 8 * st, wpar, c.wctx, code + 3)) return;
+#ifdef RINGRNN_TIMELINE
+            acc_w += clock64() - t0;
+#endif
+            tcgen05_fence_after();
+            const uint32_t a_lo = desc_lo(c.a_base + slot * CHUNK_BYTES, 16), b_lo = desc_lo(c.w_base + st * C_::WT_BYTES, 16);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              umma_ss_lo(c.tmem_base + s * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc, (half > 0 || i > 0 || ks > 0) ? 1u : 0u);
+            commit(c.bars + OFF_W_EMPTY + 8 * st);
+            if (++wst == NS) {
+              wst = 0;
+              wpar ^= 1u;
+            }
+            // nothing issued later reads the slot of this CTA's own chunk 0
+            if (half == 0 && s == 1 && i == 0) commit(c.bars + OFF_OWN0_FREE);
+          }
+          if (half == 1) {
+            commit(c.bars + OFF_D_FULL + 8 * s);
+            RINGRNN_STAMP(g, s == 0 ? 3 : 4);
+          }
+        }
+      }
+      commit(c.bars + OFF_MMA_DONE);
+      umma_commit_fanout(c.bars + OFF_ALL_FREE, (uint16_t)((1u << C_::CL) - 1u));
+      ++ph;
+    } else
 #pragma unroll
     for (int round = 0; round < R; ++round, ++ph) {
       // Will the chunks of the next phase arrive as bulk copies from peers (then their byte counts are armed here,
@@ -765,9 +850,13 @@ __device__ __forceinline__ bool publish_chunks(const Ctx<NP, PAIR>& c, const uin
 
 // Early publication, forward kernel (Cfg::EARLY).  The two chunks of a step are published separately:
 //   write_chunk   : every epilogue thread stores its 16 packed words of sub-slice s into the CTA's own A slot
-//   send_chunk    : after a barrier over the 256 epilogue threads, one thread marks the slot complete locally, copies
-//                   it to the peers and (training) stores it to the saved state with TMA.  Returns `stop` as
-//                   publish_chunks does.  `bar_id`: the named barrier to use (1 or 3).
+//   send_chunk    : (chunk 1) after a barrier over the 256 epilogue threads, one of them marks the slot complete locally,
+//                   copies it to the peers and (training) stores it to the saved state with TMA.  Returns `stop` as
+//                   publish_chunks does.
+//   sender_loop   : (chunk 0) the same hand-over done by a thread of its own (warp 3), so that no epilogue thread waits
+//                   for it: the epilogue threads arrive at named barrier 3 once their part of chunk 0 is in the slot
+//                   and go on with sub-slice 1; the sender waits there, then for "every CTA of the cluster has finished
+//                   this step's MMAs" (the peers' slots are free), and sends.
 template <int NP, bool PAIR>
 __device__ __forceinline__ void write_chunk(const Ctx<NP, PAIR>& c, const uint32_t* packed16, int s, int row, int h) {
   using C_ = Cfg<NP, PAIR>;
@@ -800,6 +889,50 @@ __device__ __forceinline__ bool send_chunk(const Ctx<NP, PAIR>& c, int s, int wa
     }
   }
   return stop;
+}
+
+constexpr uint32_t SENDER_BAR = 3, SENDER_BAR_THREADS = 288;  // 8 epilogue warps arrive, warp 3 waits
+
+// All 32 threads of warp 3 run this (named barriers are warp-wide); lane 0 does the work.  `store_y0`: row of the saved
+// state that receives the chunk of the first step of tile 0 of this cluster is y(tile, t) = (t+1)*BP + tile*TILE_ROWS.
+template <int NP, bool PAIR>
+__device__ __forceinline__ void sender_loop(const Ctx<NP, PAIR>& c, uint32_t total_steps, int T, int code,
+                                            const CUtensorMap* tm_store, int BP, int cluster_id, int n_clusters) {
+  using C_ = Cfg<NP, PAIR>;
+  using namespace tc;
+  const int lane = threadIdx.x & 31;
+  const int slot = (2 * c.q) % C_::SLOTS;
+  const uint32_t tile_addr = c.a_base + slot * CHUNK_BYTES;
+  if (tm_store != nullptr && lane == 0) tma_prefetch_desc(tm_store);
+  int t = 0, it = 0;
+  for (uint32_t g = 0; g < total_steps; ++g) {
+    const bool sends = t + 1 < T;
+    if (sends) named_bar_sync(SENDER_BAR, SENDER_BAR_THREADS);  // chunk 0 of this step is complete in the slot
+    bool ok = *c.wctx.dead == 0;
+    if (lane == 0 && ok) {
+      // one phase per step, consumed every step: every CTA of the cluster has finished this step's MMAs
+      ok = mbar_wait<true>(c.bars + OFF_ALL_FREE, g & 1u, c.wctx, code);
+      if (ok && sends) {
+        mbar_arrive(c.bars + OFF_A_FULL + 8 * slot);
+        for (int q2 = 0; q2 < C_::C; ++q2)
+          if (q2 != c.q) dsmem_bulk_copy(tile_addr, tile_addr, CHUNK_BYTES, c.bars + OFF_A_FULL + 8 * slot, c.peer_rank(q2));
+        if (tm_store != nullptr) {
+          const int tile = cluster_id + it * n_clusters;
+          tma_store_2d(tm_store, tile_addr, c.q * 128, (t + 1) * BP + tile * C_::TILE_ROWS + c.half * 128);
+          bulk_commit();
+          bulk_wait_read<0>();
+        }
+        mbar_arrive(c.bars + OFF_STORE0_DONE);
+      }
+    }
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (!ok) return;  // abandoned: the epilogue threads leave at their next publication and release this barrier
+    if (++t == T) {
+      t = 0;
+      ++it;
+    }
+  }
+  if (tm_store != nullptr && lane == 0) bulk_wait_all<0>();
 }
 
 // ---- epilogue global-memory traffic ---------------------------------------------------------------------------
