@@ -514,6 +514,7 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
   constexpr int KC = C_::KC, NS = C_::NS, SL = C_::SLOTS, R = C_::ROUNDS;
   constexpr uint32_t idesc = make_idesc_bf16(PAIR ? 256 : 128, C_::RB, 0, 0);
   constexpr bool EARLY_FWD = FWD && !GEN && C_::EARLY;
+  constexpr bool EARLY_ANY = !GEN && C_::EARLY && (FWD || NP >= 512);  // as the kernels' own EARLY flags
 #ifdef RINGRNN_NO_SPLIT
   constexpr bool SPLIT = false;
 #else
@@ -671,7 +672,7 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
             }
             // early publication: the passes start at this CTA's own chunks, so after the first tile of the last pass
             // nothing issued later reads the slot of own chunk 0: the epilogue may overwrite it once these complete
-            if (EARLY_FWD && s == 1 && grp == ng - 1 && i == 0) commit(c.bars + OFF_OWN0_FREE);
+            if (EARLY_ANY && s == 1 && grp == ng - 1 && i == 0) commit(c.bars + OFF_OWN0_FREE);
           }
           if (round == R - 1) {
             commit(c.bars + OFF_D_FULL + 8 * acc);
@@ -719,7 +720,7 @@ __device__ __forceinline__ void relay_loop(const Ctx<NP, PAIR>& c, uint32_t tota
   for (uint32_t g = 0; g < total_steps; ++g) {
     for (int round = 0; round < R; ++round, ++ph) {
       if (t == 0) tile_start(it, round);
-      if (C_::EARLY && early_acks && t != 0) {
+      if (C_::EARLY && early_acks && (!FWD || t != 0)) {  // (early_acks: the kernel's own EARLY flag)
         // early publication: chunk 0 of every peer reached this CTA as a copy out of the peer's own A slot; tell the
         // peer once it has landed, so that the peer knows when it may overwrite that slot again
         for (int q2 = 0; q2 < C_::C; ++q2)
@@ -893,9 +894,12 @@ __device__ __forceinline__ bool send_chunk(const Ctx<NP, PAIR>& c, int s, int wa
 
 constexpr uint32_t SENDER_BAR = 3, SENDER_BAR_THREADS = 288;  // 8 epilogue warps arrive, warp 3 waits
 
-// All 32 threads of warp 3 run this (named barriers are warp-wide); lane 0 does the work.  `store_y0`: row of the saved
-// state that receives the chunk of the first step of tile 0 of this cluster is y(tile, t) = (t+1)*BP + tile*TILE_ROWS.
-template <int NP, bool PAIR>
+// All 32 threads of warp 3 run this (named barriers are warp-wide); lane 0 does the work.
+// Forward: step t of a tile publishes r_t, row block t+1 of the saved state, unless it is the tile's last step.
+// Reverse: a tile first publishes delta_{T-1} (before its first step), then step t publishes delta_{t-1}, row block t-1
+// of DL, unless t = 0.  Either way the thread consumes the "every CTA has finished this step's MMAs" phase of every
+// step, so a send that follows it finds the peers' slots free.
+template <int NP, bool PAIR, bool FWD = true>
 __device__ __forceinline__ void sender_loop(const Ctx<NP, PAIR>& c, uint32_t total_steps, int T, int code,
                                             const CUtensorMap* tm_store, int BP, int cluster_id, int n_clusters) {
   using C_ = Cfg<NP, PAIR>;
@@ -904,26 +908,33 @@ __device__ __forceinline__ void sender_loop(const Ctx<NP, PAIR>& c, uint32_t tot
   const int slot = (2 * c.q) % C_::SLOTS;
   const uint32_t tile_addr = c.a_base + slot * CHUNK_BYTES;
   if (tm_store != nullptr && lane == 0) tma_prefetch_desc(tm_store);
-  int t = 0, it = 0;
+  auto send = [&](int row_block, int tile) {
+    mbar_arrive(c.bars + OFF_A_FULL + 8 * slot);
+    for (int q2 = 0; q2 < C_::C; ++q2)
+      if (q2 != c.q) dsmem_bulk_copy(tile_addr, tile_addr, CHUNK_BYTES, c.bars + OFF_A_FULL + 8 * slot, c.peer_rank(q2));
+    if (tm_store != nullptr) {
+      tma_store_2d(tm_store, tile_addr, c.q * 128, row_block * BP + tile * C_::TILE_ROWS + c.half * 128);
+      bulk_commit();
+      bulk_wait_read<0>();
+    }
+    mbar_arrive(c.bars + OFF_STORE0_DONE);
+  };
+  int t = 0, it = 0;  // step within the tile (counted upwards in both directions), tile of this cluster
   for (uint32_t g = 0; g < total_steps; ++g) {
+    const int tile = cluster_id + it * n_clusters;
+    if (!FWD && t == 0) {  // reverse: the first delta of the tile, before its first step
+      named_bar_sync(SENDER_BAR, SENDER_BAR_THREADS);
+      bool ok0 = *c.wctx.dead == 0;
+      if (lane == 0 && ok0) send(T - 1, tile);
+      if (!ok0) return;
+    }
     const bool sends = t + 1 < T;
     if (sends) named_bar_sync(SENDER_BAR, SENDER_BAR_THREADS);  // chunk 0 of this step is complete in the slot
     bool ok = *c.wctx.dead == 0;
     if (lane == 0 && ok) {
       // one phase per step, consumed every step: every CTA of the cluster has finished this step's MMAs
       ok = mbar_wait<true>(c.bars + OFF_ALL_FREE, g & 1u, c.wctx, code);
-      if (ok && sends) {
-        mbar_arrive(c.bars + OFF_A_FULL + 8 * slot);
-        for (int q2 = 0; q2 < C_::C; ++q2)
-          if (q2 != c.q) dsmem_bulk_copy(tile_addr, tile_addr, CHUNK_BYTES, c.bars + OFF_A_FULL + 8 * slot, c.peer_rank(q2));
-        if (tm_store != nullptr) {
-          const int tile = cluster_id + it * n_clusters;
-          tma_store_2d(tm_store, tile_addr, c.q * 128, (t + 1) * BP + tile * C_::TILE_ROWS + c.half * 128);
-          bulk_commit();
-          bulk_wait_read<0>();
-        }
-        mbar_arrive(c.bars + OFF_STORE0_DONE);
-      }
+      if (ok && sends) send(FWD ? t + 1 : T - 2 - t, tile);
     }
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     if (!ok) return;  // abandoned: the epilogue threads leave at their next publication and release this barrier
