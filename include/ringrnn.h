@@ -220,6 +220,23 @@ int ringrnn_angle_loss_static(int B, int T, const float* dec_x, const float* dec
                               const float* target, float bump_weight, float inv_count, float* coef_x,
                               float* coef_y, float* coef_s, float* decoded, float* loss_out, void* stream);
 
+/* Synthetic trials of the angular-velocity integration task, generated on the device (no host->device copy of inputs).
+ * Replaces, in distribution, generate_av_integration_data_ultra_fast (utils/generate_av_integration_data.py:11-58),
+ * av_to_action_signal_ND with zero padding (train_general_ring_no_gain.py:200-223) and create_initial_bump
+ * (train/train_ring_attractor.py:21-52) / the benchmark configurations' von-Mises bump:
+ *   per trial: theta0 ~ U(0,2pi); one of `zero_ratios` drawn uniformly; the first int(T*start_ratio) steps zero; of the
+ *   `rest` others exactly rest - floor(rest*ratio) stay non-zero, at uniformly drawn positions, each U(-max_av, max_av);
+ *   target[b,0] = theta0, target[b,t] = (theta0 + sum_{u<t} av[b,u]) mod 2pi;
+ *   A[b,t,:] = [relu(-av)/scale, relu(av)/scale, 0, ...]  (a_dim columns);
+ *   r_init[b,:] = bump_kind 0: exp(bump_param*(cos(2pi i/N - theta0) - 1));  1: unit-norm Gaussian of width N/bump_param.
+ * Random numbers are Philox4x32-10 with trial `first_trial + b` as the subsequence of `seed`: the same trial index gives
+ * the same trial whatever batch it is generated in (the stream is not torch's; the distribution is the reference's).
+ *   A [B,T,a_dim], target [B,T] out;  r_init [B,N] out or NULL;  theta0_scratch [B] floats (required with r_init). */
+int ringrnn_generate_trials(int B, int T, int N, int a_dim, unsigned long long seed, long long first_trial,
+                            float max_av, float scale, float start_ratio, const float* zero_ratios, int n_ratios,
+                            int bump_kind, float bump_param, float* A, float* target, float* r_init,
+                            float* theta0_scratch, void* stream);
+
 /* Optimizer step on flat buffers, entirely on the device: clip the gradient to a global L2 norm of `max_norm`
  * (max_norm <= 0: no clipping), then one Adam update (no weight decay, no amsgrad).  Replaces the pair
  * torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0); optimizer.step() of

@@ -66,6 +66,9 @@ SYMBOLS = {
     "ringrnn_angle_loss_static": (C.c_int, [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                             C.c_float, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                             C.c_void_p, C.c_void_p]),
+    "ringrnn_generate_trials": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_ulonglong, C.c_longlong, C.c_float,
+                                          C.c_float, C.c_float, C.POINTER(C.c_float), C.c_int, C.c_int, C.c_float,
+                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "ringrnn_clip_adam": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_float, C.c_float,
                                     C.c_float, C.c_float, C.c_int, C.c_float, C.c_void_p, C.c_void_p]),
     "ringrnn_device_status": (C.c_int, [C.POINTER(C.c_int)]),

@@ -56,7 +56,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     } else if (warp == 1 && lane == 0) {
       if (c.leader) mma_loop<NP, PAIR, false, GEN>(c, total_steps, T, 310, true, ng);
     } else if (warp == 2 && lane == 0) {
-      relay_loop<NP, PAIR, false>(c, total_steps, T, 320, [](int, int) {}, EARLY);
+      relay_loop<NP, PAIR, false, EARLY>(c, total_steps, T, 320, [](int, int) {});
     } else if (warp == 3) {
       if constexpr (EARLY) sender_loop<NP, PAIR, false>(c, total_steps, T, 330, &tmDL, p.BP, cluster_id, n_clusters);
     }
@@ -120,9 +120,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         }
       };
 
-      uint32_t packed[32];           // bf16 delta of the step being produced: [s*16 + w] = neurons 2w, 2w+1 of sub-slice s
-      // delta_t of sub-slice s from the carry: adds dL/dr_t and applies alpha*F'(re_t) (uses the prefetched values)
-      auto produce_half = [&](int t, int s) {
+      // delta_t of sub-slice s from the carry: adds dL/dr_t and applies alpha*F'(re_t) (uses the prefetched values).
+      // packed[s*16 + w] receives the bf16 delta of neurons 2w, 2w+1 of sub-slice s.
+      auto produce_half = [&](int t, int s, uint32_t* packed) {
         if (p.grad_output != nullptr && valid) {
           const float* gsrc = p.grad_output + ((size_t)(p.t0 + t) * p.B + b) * p.N + nq + 64 * s;
           if ((p.N & 3) == 0) {
@@ -198,7 +198,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       // [L*delta | R*delta] of sub-slice s for the weight-gradient GEMM (two active columns; off the critical path).  The
       // scaled copies are formed from the bf16 delta the MMA sees, so the three blocks are consistent with one another;
       // packed bf16 multiplies (one instruction per two elements): the action scalar is rounded to bf16 first.
-      auto dl_copies = [&](int t, int s, float Ls, float Rs) {
+      auto dl_copies = [&](int t, int s, float Ls, float Rs, const uint32_t* packed) {
         const uint32_t stage = c.stage_base + (uint32_t)(warp - 4) * 2048u;
         const size_t dl_row_bytes = (size_t)3 * NP * 2;
         // row 0 of this warp's 32-row block, first of this thread's 32 columns, column block 0
@@ -213,7 +213,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         store_rows_via_smem(stage, lane, o, blk0 + (size_t)2 * NP * 2, dl_row_bytes);
       };
       // one scaled copy per active column (weight groups): block 1 + k = A[b,t,cols[k]] * delta_t
-      auto dl_copies_generic = [&](int t) {
+      auto dl_copies_generic = [&](int t, const uint32_t* packed) {
         const uint32_t stage = c.stage_base + (uint32_t)(warp - 4) * 2048u;
         const size_t dl_row_bytes = (size_t)dl_blocks * NP * 2;
         const float* at = p.A + ((size_t)b * p.T_total + p.t0 + t) * p.a_dim;
@@ -235,7 +235,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       };
 
       // early publication of chunk 0 of delta_t: into this CTA's own slot, then over to the sender thread
-      auto hand_over_chunk0 = [&]() {
+      auto hand_over_chunk0 = [&](const uint32_t* packed) {
         while (sent_waited < n_sent) {  // the previous copies out of that slot have arrived, the TMA store has read it
           mbar_wait<true>(bars + OFF_SENT_DONE, sent_waited & 1u, wctx, 309);
           mbar_wait(bars + OFF_STORE0_DONE, sent_waited & 1u, wctx, 309);
@@ -246,7 +246,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         ++n_sent;
       };
       // chunk 1 of delta_t: write, then one epilogue thread sends it (delta_t is also column block 0 of DL row block t)
-      auto publish_chunk1 = [&](int t) {
+      auto publish_chunk1 = [&](int t, const uint32_t* packed) {
         if (warp == 4 && lane == 0) bulk_wait_read<0>();  // the TMA stores issued so far have read the slot
         named_bar_sync(2, 256);
         write_chunk<NP, PAIR>(c, packed + 16, 1, row, h);
@@ -255,35 +255,37 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 
       // delta_t for both sub-slices at once, published together (CTA pairs, two K rounds, weight groups, one slice)
       auto produce = [&](int t) {
+        uint32_t packed[32];
         L = Ln;
         R = Rn;
-        produce_half(t, 0);
-        produce_half(t, 1);
+        produce_half(t, 0, packed);
+        produce_half(t, 1, packed);
         // delta_t: A operand of this step everywhere, and column block 0 of DL row block t (TMA store from the chunks)
         stop = publish_chunks<NP, PAIR>(c, packed, row, h, warp, lane, &tmDL, q * 128,
                                         t * p.BP + tile * C_::TILE_ROWS + c.half * 128);
         if (stop) return;
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 12);
         if constexpr (!GEN) {
-          dl_copies(t, 0, L, R);
-          dl_copies(t, 1, L, R);
+          dl_copies(t, 0, L, R, packed);
+          dl_copies(t, 1, L, R, packed);
         } else {
-          dl_copies_generic(t);
+          dl_copies_generic(t, packed);
         }
       };
 
       prefetch(T - 1);
       freed.before_publish(c, g, rq, 308);
       if constexpr (EARLY) {
-        produce_half(T - 1, 0);
-        hand_over_chunk0();
-        produce_half(T - 1, 1);
-        publish_chunk1(T - 1);
+        uint32_t packed[32];
+        produce_half(T - 1, 0, packed);
+        hand_over_chunk0(packed);
+        produce_half(T - 1, 1, packed);
+        publish_chunk1(T - 1, packed);
         if (stop) break;
         L = Ln;
         R = Rn;
-        dl_copies(T - 1, 0, L, R);
-        dl_copies(T - 1, 1, L, R);
+        dl_copies(T - 1, 0, L, R, packed);
+        dl_copies(T - 1, 1, L, R, packed);
       } else {
         produce(T - 1);
         if (stop) break;
@@ -291,6 +293,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       for (int t = T - 1; t >= 0; --t, ++g) {
         if (t > 0) prefetch(t - 1);
         float c0 = 0.f, dAl = 0.f, dAr = 0.f;
+        uint32_t packed[EARLY ? 32 : 1];  // (early publication) bf16 delta_{t-1}, produced sub-slice by sub-slice
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
           if constexpr (GEN) {
@@ -420,9 +423,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               if (t > 0) {
                 // the carry of sub-slice 0 is complete: its delta goes out while accumulator 1 is still being filled,
                 // and its scaled copies are written in the wait for that accumulator
-                produce_half(t - 1, 0);
-                hand_over_chunk0();
-                dl_copies(t - 1, 0, Ln, Rn);
+                produce_half(t - 1, 0, packed);
+                hand_over_chunk0(packed);
+                dl_copies(t - 1, 0, Ln, Rn, packed);
               }
             }
           }
@@ -438,13 +441,13 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 10);
         if (t > 0) {
           if constexpr (EARLY) {
-            produce_half(t - 1, 1);
-            publish_chunk1(t - 1);
+            produce_half(t - 1, 1, packed);
+            publish_chunk1(t - 1, packed);
             if (stop) break;
             if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 12);
             L = Ln;
             R = Rn;
-            dl_copies(t - 1, 1, L, R);
+            dl_copies(t - 1, 1, L, R, packed);
           } else {
             produce(t - 1);
             if (stop) break;

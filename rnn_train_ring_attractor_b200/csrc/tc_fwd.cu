@@ -51,7 +51,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       if (c.leader) mma_loop<NP, PAIR, true, GEN>(c, total_steps, T, 210, p.Rh != nullptr, ng);
     } else if (warp == 2 && lane == 0) {
       tma_prefetch_desc(&tmR0);
-      relay_loop<NP, PAIR, true>(c, total_steps, T, 220, [&](int it, int round) {
+      relay_loop<NP, PAIR, true, EARLY>(c, total_steps, T, 220, [&](int it, int round) {
         // initial state of the tile: this CTA's 128 samples, the K chunks of this round (the MMAs that read the
         // slots before are done: the relay has seen every phase of mma_done)
         const int tile = cluster_id + it * n_clusters;
@@ -60,7 +60,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           tma_load_2d(a_base + slot * CHUNK_BYTES, &tmR0, bars + OFF_A_FULL + 8 * slot, (round * C_::SLOTS + slot) * 64,
                       tile * C_::TILE_ROWS + c.half * 128);
         }
-      }, EARLY);
+      });
     } else if (warp == 3) {
       if constexpr (EARLY)
         sender_loop<NP, PAIR>(c, total_steps, T, 230, p.Rh != nullptr ? &tmR0 : nullptr, p.BP, cluster_id, n_clusters);

@@ -196,3 +196,23 @@ def test_device_status_surface_without_a_gpu(L):
     assert L.ringrnn_selftest_wait(-1, 7, 1, None) == 1           # negative limit
     assert L.ringrnn_selftest_wait(1000, 0, 1, None) == 1         # code 0 would be indistinguishable from success
     _lib.raise_if_device_error()
+
+
+def test_generate_trials_validates_arguments(L):
+    ratios = (C.c_float * 3)(0.2, 0.5, 0.8)
+    ok = [8, 10, 16, 2, 1, 0, 0.3, 0.3, 0.1, ratios, 3, 0, 4.0, 1, 1, 1, 1, None]
+
+    def call(**kw):
+        a = list(ok)
+        for i, v in kw.items():
+            a[int(i[1:])] = v
+        return L.ringrnn_generate_trials(*a)
+
+    assert call(_0=0) == 2            # no trials
+    assert call(_13=None) == 1        # A missing
+    assert call(_10=9) == 1           # more zero-ratios than the library holds
+    assert call(_6=0.0) == 1          # max_av must be positive
+    assert call(_11=2) == 1           # unknown bump kind
+    assert call(_16=None) == 1        # r_init without the theta0 scratch
+    bad = (C.c_float * 3)(0.2, 1.5, 0.8)
+    assert call(_9=bad) == 1          # a zero-ratio outside [0, 1]
