@@ -46,8 +46,8 @@ WORKLOADS = {
 # under profiles/ (taken at T=64, B=4096; traffic is proportional to B*T).  None = no capture for that kernel/mode.
 NCU_CAPTURE_SOURCE = "ncu captures at T=64 summarised in profiles/{fwd,bwd}_tc_kernel_c3_T64.md, gemm_tc_kernel_dw_c3_T64.md"
 NCU_DRAM_BYTES_PER_SAMPLE_STEP = {
-    ("bf16", 512): {"fwd_recurrent": (16.50e6 + 544.22e6) / (4096 * 64), "bwd_recurrent": (309.06e6 + 750.17e6) / (4096 * 64),
-                    "dw_product": (1074.0e6 + 3.95e6) / (4096 * 64)},
+    ("bf16", 512): {"fwd_recurrent": (16.52e6 + 544.40e6) / (4096 * 64), "bwd_recurrent": (309.17e6 + 751.74e6) / (4096 * 64),
+                    "dw_product": (1074.06e6 + 3.61e6) / (4096 * 64)},
 }
 METRIC = "fwd+bwd sample-timesteps/s"
 UNIT = "sample-timesteps/s"
@@ -307,6 +307,49 @@ def run_published_table(args):
           flush=True)
 
 
+def run_timeline(args, wl):
+    """In-kernel timeline of one CTA of the forward and of the reverse-time kernel (diagnostic; needs the library built by
+    `python -m rnn_train_ring_attractor_b200.build --timeline`).  Prints, for a few steps in the steady state, the cycle
+    at which each role passed each point of a step, relative to the step's first stamp:
+      mma: pass start / first own chunk present / second half or pass start / accumulator 0, 1 committed
+      epilogue (warp 4): accumulator 0, 1 seen complete / read out / arithmetic of sub-slice 1 done / peers' slots free /
+      chunk published;  WAIT_W, WAIT_A: cycles the MMA-issuing thread spent waiting for weight stages and state chunks."""
+    import ctypes as C
+    from rnn_train_ring_attractor_b200 import _lib
+    from rnn_train_ring_attractor_b200.build import TIMELINE_LIB
+    if not os.path.exists(TIMELINE_LIB):
+        raise RuntimeError("build the diagnostic library first: python -m rnn_train_ring_attractor_b200.build --timeline")
+    _lib.LIB_PATH = TIMELINE_LIB
+    from rnn_train_ring_attractor_b200.fused import ring_rnn_fused
+    from rnn_train_ring_attractor_b200.inputs import benchmark_inputs
+    torch.cuda.set_device(0)
+    N, B, T, act = wl["N"], wl["B"], min(wl["T"], 64), wl["act"]
+    d = benchmark_inputs(N, B, T, seed=0, max_av=wl["max_av"], device="cuda")
+    for _ in range(2):
+        Wa, Wo = d["Wa"].clone().requires_grad_(True), d["Wo"].clone().requires_grad_(True)
+        loss, _, _, _ = ring_rnn_fused(d["A"], Wa, -0.1, 0.1, Wo, d["r_init"], 0.1, act, d["target"], precision="bf16")
+        loss.backward()
+    torch.cuda.synchronize()
+    h = C.CDLL(TIMELINE_LIB)
+    names = {"forward": ["mma:start", "mma:own_chunk", "mma:2nd_half", "mma:commit0", "mma:commit1", "epi:dfull0", "epi:read0",
+                         "epi:dfull1", "epi:read1", "epi:math1_done", "epi:slots_free", "epi:published"],
+             "reverse": ["mma:start", "mma:own_chunks", "mma:pass1", "mma:commit0", "mma:commit1", "epi:dfull0", "epi:read0",
+                         "epi:dfull1", "epi:read1", "epi:carry_done", "epi:slots_free", "epi:DL_written", "epi:published"]}
+    out = {"workload": f"{args.workload}: N={N}, B={B}, T={T}, {act}", "unit": "SM cycles relative to the step's first stamp"}
+    for kernel, fn in (("forward", h.ringrnn_debug_timeline_read), ("reverse", h.ringrnn_debug_timeline_read_bwd)):
+        buf = (C.c_longlong * (64 * 16))()
+        if fn(buf) != 0:
+            raise RuntimeError("reading the timeline failed")
+        steps = []
+        for g in (20, 21, 22, 40):
+            base = buf[g * 16]
+            row = {n: int(buf[g * 16 + i] - base) for i, n in enumerate(names[kernel])}
+            row.update(step=g, next_step_start=int(buf[(g + 1) * 16] - base), WAIT_W=int(buf[g * 16 + 13]), WAIT_A=int(buf[g * 16 + 14]))
+            steps.append(row)
+        out[kernel] = steps
+    print(json.dumps(out), flush=True)
+
+
 def run_ours(args, wl):
     import torch.distributed as dist
     from rnn_train_ring_attractor_b200 import _lib, dp
@@ -504,6 +547,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--seq-len", type=int, default=0, help="override T (profiling on a smaller case of the same kernels)")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="diagnostic: print the in-kernel timeline of the recurrent kernels (needs the --timeline build)")
     ap.add_argument("--ckpt-every", type=int, default=0,
                     help="keep the state every K steps and recompute in backward (0 = keep every step)")
     args = ap.parse_args()
@@ -515,7 +560,9 @@ def main():
         wl["T"] = args.seq_len
     if args.batch:
         wl["B"] = args.batch
-    if args.impl == "reference":
+    if args.timeline:
+        run_timeline(args, wl)
+    elif args.impl == "reference":
         run_reference(args, wl)
     elif wl.get("rollout"):
         run_rollout(args, wl)

@@ -29,6 +29,31 @@ def _deps_mtime():
     return max(os.path.getmtime(f) for f in files)
 
 
+TIMELINE_LIB = os.path.join(PKG, "libringrnn_timeline.so")
+
+
+def build_timeline():
+    """The same library with the in-kernel timeline compiled in (-DRINGRNN_TIMELINE: cycle stamps of one CTA of each
+    recurrent kernel, read with ringrnn_debug_timeline_read*; see `bench.py --timeline`).  A diagnostic build: the
+    stamps cost a few percent, so it is never the library the operator loads."""
+    nvcc = os.environ.get("NVCC") or os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+    objdir = os.path.join(OBJ, "timeline")
+    os.makedirs(objdir, exist_ok=True)
+    procs, objs = [], []
+    for src in sources():
+        obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
+        objs.append(obj)
+        procs.append((src, subprocess.Popen([nvcc] + NVCC_FLAGS + ["-DRINGRNN_TIMELINE", "-c", src, "-o", obj],
+                                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    for src, pr in procs:
+        out, _ = pr.communicate()
+        if pr.returncode != 0:
+            sys.stderr.write(out)
+            raise RuntimeError(f"nvcc failed on {src}")
+    subprocess.run([nvcc, "-shared", "-o", TIMELINE_LIB] + objs, check=True)
+    return TIMELINE_LIB
+
+
 def build(force=False, verbose=False):
     """Compile every .cu under csrc/ into libringrnn.so; skipped when the library is newer than all sources."""
     if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _deps_mtime():
@@ -58,4 +83,7 @@ def build(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--timeline" in sys.argv:
+        print(build_timeline())
+    else:
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
