@@ -96,7 +96,6 @@ __global__ void dec_reduce_kernel(const float* __restrict__ part, int slots, int
 
 struct Layout {
   int NP, BP, C, RB, tile_rows;
-  int wbox_cols;   // k-columns of one weight stage (tc_recurrent.cuh, Cfg::KT)
   int n_act, ng;   // active action columns; weight groups of three matrices (1 for up to two columns)
   bool pair;
   size_t w_bytes, r0_bytes, dec_bytes, state_bytes;
@@ -111,7 +110,6 @@ Layout layout_of(const RingRnnProblem& p) {
   l.ng = l.n_act <= 2 ? 1 : (1 + l.n_act + 2) / 3;
   l.pair = use_pairs(p.B, p.N) && l.ng == 1;
   l.RB = block_rows(l.pair);
-  l.wbox_cols = weight_stage_cols(l.NP, l.pair);
   l.tile_rows = l.pair ? 256 : 128;
   l.w_bytes = align_up((size_t)l.C * 2 * l.ng * l.RB * l.NP * 2, 1024);
   l.r0_bytes = align_up((size_t)l.BP * l.NP * 2, 1024);
@@ -201,7 +199,7 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   RINGRNN_CUDA_TRY(cudaGetLastError());
 
   CUtensorMap tmW, tmR0;
-  if (!make_tmap_bf16_2d(&tmW, Wf, (uint64_t)l.C * 2 * l.ng * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, l.wbox_cols, l.wbox_cols == 32 ? 64 : 128))
+  if (!make_tmap_bf16_2d(&tmW, Wf, (uint64_t)l.C * 2 * l.ng * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, 64))
     return RINGRNN_ERR_CUDA;
   // one map serves the initial-state loads (rows [0, BP)) and, in training, the saved-state stores (rows up to T*BP)
   if (!make_tmap_bf16_2d(&tmR0, R0, (uint64_t)(keep_all ? p.T + 1 : 1) * l.BP, (uint64_t)l.NP, 128, 64))
@@ -377,8 +375,8 @@ int bf16_backward_ckpt(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream
   }
   RINGRNN_CUDA_TRY(cudaGetLastError());
   CUtensorMap tmWf, tmWb;
-  if (!make_tmap_bf16_2d(&tmWf, Wf, (uint64_t)l.C * 2 * l.ng * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, l.wbox_cols, l.wbox_cols == 32 ? 64 : 128) ||
-      !make_tmap_bf16_2d(&tmWb, Wb, (uint64_t)l.C * 2 * l.ng * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, l.wbox_cols, l.wbox_cols == 32 ? 64 : 128))
+  if (!make_tmap_bf16_2d(&tmWf, Wf, (uint64_t)l.C * 2 * l.ng * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, 64) ||
+      !make_tmap_bf16_2d(&tmWb, Wb, (uint64_t)l.C * 2 * l.ng * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, 64))
     return RINGRNN_ERR_CUDA;
   if (a.grad_A != nullptr)
     RINGRNN_CUDA_TRY(cudaMemsetAsync(a.grad_A, 0, sizeof(float) * (size_t)p.B * p.T * p.a_dim, s));
@@ -507,7 +505,7 @@ int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   }
   RINGRNN_CUDA_TRY(cudaGetLastError());
   CUtensorMap tmW;
-  if (!make_tmap_bf16_2d(&tmW, Wb, (uint64_t)l.C * 2 * l.ng * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, l.wbox_cols, l.wbox_cols == 32 ? 64 : 128))
+  if (!make_tmap_bf16_2d(&tmW, Wb, (uint64_t)l.C * 2 * l.ng * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, 64))
     return RINGRNN_ERR_CUDA;
 
   TcBwdParams bp;

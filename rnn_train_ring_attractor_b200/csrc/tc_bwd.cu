@@ -253,23 +253,134 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         stop = send_chunk<NP, PAIR>(c, 1, warp, lane, 1, &tmDL, q * 128, t * p.BP + tile * C_::TILE_ROWS + c.half * 128);
       };
 
-      // delta_t for both sub-slices at once, published together (CTA pairs, two K rounds, weight groups, one slice)
+      // Both sub-slices at once, published together (CTA pairs, two K rounds, weight groups, a single slice, N = 256):
+      // delta_t from the carry: adds dL/dr_t, applies alpha*F'(re_t), publishes the bf16 chunks, writes DL
       auto produce = [&](int t) {
-        uint32_t packed[32];
         L = Ln;
         R = Rn;
-        produce_half(t, 0, packed);
-        produce_half(t, 1, packed);
+        if (p.grad_output != nullptr && valid) {
+#pragma unroll
+          for (int s = 0; s < 2; ++s) {
+            const float* gsrc = p.grad_output + ((size_t)(p.t0 + t) * p.B + b) * p.N + nq + 64 * s;
+            if ((p.N & 3) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                if (nq + 64 * s + j < p.N) {
+                  const float4 gv = __ldg(reinterpret_cast<const float4*>(gsrc + j));
+                  master[s * 32 + j] += gv.x; master[s * 32 + j + 1] += gv.y;
+                  master[s * 32 + j + 2] += gv.z; master[s * 32 + j + 3] += gv.w;
+                }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nq + 64 * s + j < p.N) master[s * 32 + j] += __ldg(gsrc + j);
+            }
+          }
+        }
+        uint32_t packed[32];
+        const f32x2 cxp = pk2(cx, cx), cyp = pk2(cy, cy), onep = pk2(1.f, 1.f), alphap = pk2(alpha, alpha);
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          // d|r|/dr = sign(r_t) is applied below as +cs or -cs by the sign bit alone (two instructions per element);
+          // where r_t is an exact zero (rare; always so for padding columns) the term must vanish: take it out of
+          // the carry beforehand
+          if (has_coef && mzero[s] != 0u) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (mzero[s] & (1u << j)) master[s * 32 + j] -= (mneg[s] & (1u << j)) ? -cs : cs;
+          }
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint32_t dw[4] = {dv[s * 4 + v].x, dv[s * 4 + v].y, dv[s * 4 + v].z, dv[s * 4 + v].w};
+            // the eight decode weights of this group in four 16-byte shared-memory loads (same address in every lane)
+            float uu[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, vv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (has_coef) {
+              const float4* up = reinterpret_cast<const float4*>(uv + 64 * s + 32 * h + 8 * v);
+              const float4* vp = reinterpret_cast<const float4*>(uv + 128 + 64 * s + 32 * h + 8 * v);
+              const float4 u0 = up[0], u1 = up[1], v0 = vp[0], v1 = vp[1];
+              uu[0] = u0.x; uu[1] = u0.y; uu[2] = u0.z; uu[3] = u0.w; uu[4] = u1.x; uu[5] = u1.y; uu[6] = u1.z; uu[7] = u1.w;
+              vv[0] = v0.x; vv[1] = v0.y; vv[2] = v0.z; vv[3] = v0.w; vv[4] = v1.x; vv[5] = v1.y; vv[6] = v1.z; vv[7] = v1.w;
+            }
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {  // two neurons at a time
+              const int j = v * 8 + w * 2;
+              const int idx = s * 32 + j;
+              if constexpr (PACKED) {
+                f32x2 gg = pk2(master[idx], master[idx + 1]);
+                if (has_coef) {
+                  gg = fma2(cxp, pk2(uu[w * 2], uu[w * 2 + 1]), gg);
+                  gg = fma2(cyp, pk2(vv[w * 2], vv[w * 2 + 1]), gg);
+                  // + cs * sign(r_t) by the sign bit; exact zeros were pre-compensated
+                  gg = fma2(onep, pk2((mneg[s] & (1u << j)) ? -cs : cs, (mneg[s] & (2u << j)) ? -cs : cs), gg);
+                }
+                upk2(gg, master[idx], master[idx + 1]);
+                float d0, d1;
+                upk2(mul2(mul2(alphap, pk2(bf16_lo(dw[w]), bf16_hi(dw[w]))), gg), d0, d1);
+                packed[s * 16 + v * 4 + w] = pack_bf16x2(d0, d1);
+              } else {
+                float dl[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                  float gg = master[idx + e];
+                  if (has_coef) {
+                    gg = fmaf(cx, uu[w * 2 + e], gg);
+                    gg = fmaf(cy, vv[w * 2 + e], gg);
+                    gg += (mneg[s] & (1u << (j + e))) ? -cs : cs;  // + cs * sign(r_t); exact zeros were pre-compensated
+                  }
+                  master[idx + e] = gg;
+                  dl[e] = alpha * (e ? bf16_hi(dw[w]) : bf16_lo(dw[w])) * gg;
+                }
+                packed[s * 16 + v * 4 + w] = pack_bf16x2(dl[0], dl[1]);
+              }
+            }
+          }
+        }
         // delta_t: A operand of this step everywhere, and column block 0 of DL row block t (TMA store from the chunks)
         stop = publish_chunks<NP, PAIR>(c, packed, row, h, warp, lane, &tmDL, q * 128,
                                         t * p.BP + tile * C_::TILE_ROWS + c.half * 128);
         if (stop) return;
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 12);
+        // off the critical path: [delta | L*delta | R*delta] for the weight-gradient GEMM.  The scaled copies are
+        // formed from the bf16 delta the MMA sees, so the three blocks are consistent with one another.
+        const uint32_t stage = c.stage_base + (uint32_t)(warp - 4) * 2048u;
+        const size_t dl_row_bytes = (size_t)dl_blocks * NP * 2;
         if constexpr (!GEN) {
-          dl_copies(t, 0, L, R, packed);
-          dl_copies(t, 1, L, R, packed);
+          // packed bf16 multiplies (one instruction per two elements): the action scalar is rounded to bf16 first
+#pragma unroll
+          for (int s = 0; s < 2; ++s) {
+            // row 0 of this warp's 32-row block, first of this thread's 32 columns, column block 0
+            uint8_t* blk0 = reinterpret_cast<uint8_t*>(p.DL + ((size_t)t * p.BP + (b - lane)) * (3 * NP) + nq + 64 * s);
+            const uint32_t L2 = pack_bf16x2(L, L), R2 = pack_bf16x2(R, R);
+            uint32_t o[16];
+#pragma unroll
+            for (int w = 0; w < 16; ++w) {
+              o[w] = mul_bf16x2(packed[s * 16 + w], L2);
+            }
+            store_rows_via_smem(stage, lane, o, blk0 + (size_t)NP * 2, dl_row_bytes);
+#pragma unroll
+            for (int w = 0; w < 16; ++w) {
+              o[w] = mul_bf16x2(packed[s * 16 + w], R2);
+            }
+            store_rows_via_smem(stage, lane, o, blk0 + (size_t)2 * NP * 2, dl_row_bytes);
+          }
         } else {
-          dl_copies_generic(t, packed);
+          // one scaled copy per active column: block 1 + k = A[b,t,cols[k]] * delta_t
+          const float* at = p.A + ((size_t)b * p.T_total + p.t0 + t) * p.a_dim;
+          for (int k = 0; k < p.n_act; ++k) {
+            const float ak = valid ? __ldg(at + p.cols[k]) : 0.f;
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+              uint8_t* blk0 = reinterpret_cast<uint8_t*>(p.DL + ((size_t)t * p.BP + (b - lane)) * ((size_t)dl_blocks * NP) +
+                                                         nq + 64 * s);
+              uint32_t o[16];
+#pragma unroll
+              for (int w = 0; w < 16; ++w) {
+                const uint32_t d2 = packed[s * 16 + w];
+                o[w] = pack_bf16x2(ak * bf16_lo(d2), ak * bf16_hi(d2));
+              }
+              store_rows_via_smem(stage, lane, o, blk0 + (size_t)(1 + k) * NP * 2, dl_row_bytes);
+            }
+          }
         }
       };
 

@@ -347,9 +347,6 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
 // 32 bits are constant (SBO = 1024, version, swizzle mode), the lower 32 bits are address >> 4 plus LBO >> 4 at bit 16;
 // stepping along K inside a K-major tile adds 2 (32 bytes) to the lower half, along an MN-major tile 128 (2048 bytes).
 constexpr uint32_t DESC_HI_SW128 = (1024u >> 4) | (1u << 14) | (2u << 29);
-// K-major operand in the 64-byte swizzle (what a TMA box with a 64-byte inner extent and CU_TENSOR_MAP_SWIZZLE_64B writes;
-// 32 bf16 of K per 64-byte row, tile base 512-byte aligned): SBO = 512 (8 rows), layout type 4.
-constexpr uint32_t DESC_HI_SW64 = (512u >> 4) | (1u << 14) | (4u << 29);
 __device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
   return ((saddr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
 }
@@ -365,21 +362,6 @@ __device__ __forceinline__ void umma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint3
       "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
       "}\n" ::"r"(d_tmem),
       "r"(a_lo), "r"(b_lo), "r"(DESC_HI_SW128), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// the same with separate upper halves for A and B (operands in different swizzle modes)
-__device__ __forceinline__ void umma_ss_lo2(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
-                                            uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      ".reg .b64 da, db;\n\t"
-      "setp.ne.b32 p, %6, 0;\n\t"
-      "mov.b64 da, {%1, %2};\n\t"
-      "mov.b64 db, {%3, %4};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
-      "}\n" ::"r"(d_tmem),
-      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void umma_ss_pair_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
@@ -414,8 +396,7 @@ __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t k) {
 // ---- host: tensor maps ------------------------------------------------------------------------------
 // 2-D bf16 row-major tensor [rows, cols] (cols contiguous), box = [box_rows, box_cols], 128-byte swizzle.
 // Returns false if the driver entry point is unavailable or the encode fails.
-// `swizzle_bytes`: 128 (inner box extent 64 elements) or 64 (inner box extent 32 elements).
 bool make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                       uint32_t box_cols, int swizzle_bytes = 128);
+                       uint32_t box_cols);
 
 }  // namespace ringrnn

@@ -142,22 +142,14 @@ struct Cfg {
   static constexpr int ROUNDS = KC / SLOTS;      // K rounds per step
   static constexpr int RB = block_rows(PAIR);    // rows of one weight block = accumulator columns used
   static constexpr int WROWS = PAIR ? RB / 2 : RB;  // rows of a weight tile this CTA loads
-  // Weight stages.  The weights of a step (416 KB per CTA at N = 512) stream from L2 through a ring of stages of 64
-  // k-columns (26 KB; three of them fit beside the state operand at N >= 512).  Stages of 32 k-columns in the 64-byte
-  // swizzle (six of 13 KB: 65 instead of 52 KB in flight) are implemented behind -DRINGRNN_HALFK and pass the parity
-  // suite, but measured SLOWER (N = 512, B = 4096, T = 512: forward 6.14 against 5.16 ms, reverse 6.69 against 5.80 ms;
-  // N = 1024: +16 %): twice as many waits and commits for the one thread that issues the MMAs cost more than the extra
-  // bytes in flight bring -- that thread's per-stage work, not the L2 latency of the stream, bounds the passes.
-#ifdef RINGRNN_HALFK
-  static constexpr bool HALFK = !PAIR && NP >= 512;
-#else
-  static constexpr bool HALFK = false;
-#endif
-  static constexpr int KT = HALFK ? 32 : 64;     // k-columns per weight stage
-  static constexpr int KH = 64 / KT;             // stages per 64-column chunk of the state
-  static constexpr int WT_BYTES = WROWS * KT * 2;   // one [WROWS x KT] bf16 tile
+  // Weight stages: [WROWS x 64] tiles of 26 KB, filled by tiled TMA loads.  Two variations were built, passed the parity
+  // suite and were taken out again because they measured slower: stages of 32 k-columns in the 64-byte swizzle (six of
+  // 13 KB instead of three of 26 KB at N = 512: forward 6.14 against 5.16 ms) and weights stored tile by tile in the
+  // shared-memory layout so that one untiled bulk copy fills a stage (N = 512 unchanged, N = 1024 13 % slower).  The
+  // stream is bound by the rate at which data enters an SM (about 50 B/clk, whatever the ring depth), not by latency.
+  static constexpr int WT_BYTES = WROWS * 128;   // one [WROWS x 64] bf16 tile
   static constexpr int A_BYTES = SLOTS * CHUNK_BYTES;
-  static constexpr int TILES = 2 * KC * KH;      // weight tiles per step
+  static constexpr int TILES = 2 * KC;           // weight tiles per step
   static constexpr int AUX = 2048;               // barriers, flags, decode vectors
   static constexpr int STAGE_BYTES = 8 * 2048;   // one 32-row x 64-byte transposition buffer per epilogue warp
   static constexpr int NS_FIT = (SMEM_LIMIT - 1024 - AUX - STAGE_BYTES - A_BYTES) / WT_BYTES;
@@ -468,12 +460,12 @@ __device__ __forceinline__ void producer_loop(const Ctx<NP, PAIR>& c, const CUte
   if (total_steps == 0) return;
   const uint64_t keep = l2_policy_evict_last();
   const int rot = (2 * c.q) % SL;
-  auto issue = [&](int st, int s, int grp, int kc, int kh = 0) {
+  auto issue = [&](int st, int s, int grp, int kc) {
     const uint32_t bar = c.bars + OFF_W_FULL + 8 * st;
     const int y = ((c.q * 2 + s) * ng + grp) * C_::RB + c.half * C_::WROWS;
     if (c.leader) mbar_arrive_expect_tx(bar, (PAIR ? 2 : 1) * C_::WT_BYTES);  // a pair's two halves land on one barrier
     if (PAIR) tma_load_2d_pair(c.w_base + st * C_::WT_BYTES, tmW, bar, kc * 64, y);
-    else tma_load_2d_hint(c.w_base + st * C_::WT_BYTES, tmW, bar, kc * 64 + kh * C_::KT, y, keep);
+    else tma_load_2d_hint(c.w_base + st * C_::WT_BYTES, tmW, bar, kc * 64, y, keep);
   };
   if (C_::RESIDENT && ng == 1) {
     for (int s = 0; s < 2; ++s)
@@ -485,15 +477,14 @@ __device__ __forceinline__ void producer_loop(const Ctx<NP, PAIR>& c, const CUte
       for (int half = 0; half < 2; ++half)
         for (int s = 0; s < 2; ++s)
 #pragma unroll 1
-          for (int i = half; i < SL; i += 2)
-            for (int kh = 0; kh < C_::KH; ++kh) {
-              if (lap > 0 && !mbar_wait(c.bars + OFF_W_EMPTY + 8 * st, (lap - 1) & 1u, c.wctx, code)) return;
-              issue(st, s, 0, (rot + i) % SL, kh);
-              if (++st == NS) {
-                st = 0;
-                ++lap;
-              }
+          for (int i = half; i < SL; i += 2) {
+            if (lap > 0 && !mbar_wait(c.bars + OFF_W_EMPTY + 8 * st, (lap - 1) & 1u, c.wctx, code)) return;
+            issue(st, s, 0, (rot + i) % SL);
+            if (++st == NS) {
+              st = 0;
+              ++lap;
             }
+          }
   } else {
     int st = 0;              // ring stage of the next tile
     uint32_t lap = 0;        // how many times the ring has been filled
@@ -502,16 +493,15 @@ __device__ __forceinline__ void producer_loop(const Ctx<NP, PAIR>& c, const CUte
         for (int s = 0; s < 2; ++s)
           for (int grp = 0; grp < ng; ++grp)
 #pragma unroll 1
-            for (int i = 0; i < SL; ++i)
-              for (int kh = 0; kh < C_::KH; ++kh) {
-                if (lap > 0 && !mbar_wait(c.bars + OFF_W_EMPTY + 8 * st, (lap - 1) & 1u, c.wctx, code))
-                  return;  // abandoned: issue nothing more
-                issue(st, s, grp, round * SL + (rot + i) % SL, kh);
-                if (++st == NS) {
-                  st = 0;
-                  ++lap;
-                }
+            for (int i = 0; i < SL; ++i) {
+              if (lap > 0 && !mbar_wait(c.bars + OFF_W_EMPTY + 8 * st, (lap - 1) & 1u, c.wctx, code))
+                return;  // abandoned: issue nothing more
+              issue(st, s, grp, round * SL + (rot + i) % SL);
+              if (++st == NS) {
+                st = 0;
+                ++lap;
               }
+            }
   }
 }
 
@@ -528,7 +518,6 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
   using namespace tc;
   constexpr int KC = C_::KC, NS = C_::NS, SL = C_::SLOTS, R = C_::ROUNDS;
   constexpr uint32_t idesc = make_idesc_bf16(PAIR ? 256 : 128, C_::RB, 0, 0);
-  constexpr uint32_t B_HI = C_::HALFK ? DESC_HI_SW64 : DESC_HI_SW128;  // swizzle mode of the weight stages
   constexpr bool EARLY_FWD = FWD && !GEN && C_::EARLY;
   constexpr bool EARLY_ANY = !GEN && C_::EARLY && (FWD || NP >= 512);  // as the kernels' own EARLY flags
 #ifdef RINGRNN_NO_SPLIT
@@ -582,39 +571,23 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
 #endif
               if (next_by_copy && (slot >> 1) != c.q) mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * slot, CHUNK_BYTES);
             }
-            auto stage_mmas = [&](int kh) -> bool {
-              const int st = wst;
+            const int st = wst;
 #ifdef RINGRNN_TIMELINE
-              t0 = clock64();
+            t0 = clock64();
 #endif
-              if (!mbar_wait(c.bars + OFF_W_FULL + 8 * st, wpar, c.wctx, code + 3)) return false;
+            if (!mbar_wait(c.bars + OFF_W_FULL + 8 * st, wpar, c.wctx, code + 3)) return;
 #ifdef RINGRNN_TIMELINE
-              acc_w += clock64() - t0;
+            acc_w += clock64() - t0;
 #endif
-              tcgen05_fence_after();
-              const uint32_t a_lo = desc_lo(c.a_base + slot * CHUNK_BYTES, 16) + 2 * (C_::KT / 16) * kh,
-                             b_lo = desc_lo(c.w_base + st * C_::WT_BYTES, 16);
+            tcgen05_fence_after();
+            const uint32_t a_lo = desc_lo(c.a_base + slot * CHUNK_BYTES, 16), b_lo = desc_lo(c.w_base + st * C_::WT_BYTES, 16);
 #pragma unroll
-              for (int ks = 0; ks < C_::KT / 16; ++ks)
-                if constexpr (C_::HALFK)
-                  umma_ss_lo2(c.tmem_base + s * 256, a_lo + 2 * ks, DESC_HI_SW128, b_lo + 2 * ks, B_HI, idesc,
-                              (half > 0 || i > 0 || kh > 0 || ks > 0) ? 1u : 0u);
-                else
-                  umma_ss_lo(c.tmem_base + s * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc,
-                             (half > 0 || i > 0 || kh > 0 || ks > 0) ? 1u : 0u);
-              commit(c.bars + OFF_W_EMPTY + 8 * st);
-              if (++wst == NS) {
-                wst = 0;
-                wpar ^= 1u;
-              }
-              return true;
-            };
-            if constexpr (C_::KH == 1) {
-              if (!stage_mmas(0)) return;
-            } else {
-#pragma unroll 1
-              for (int kh = 0; kh < C_::KH; ++kh)
-                if (!stage_mmas(kh)) return;
+            for (int ks = 0; ks < 4; ++ks)
+              umma_ss_lo(c.tmem_base + s * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc, (half > 0 || i > 0 || ks > 0) ? 1u : 0u);
+            commit(c.bars + OFF_W_EMPTY + 8 * st);
+            if (++wst == NS) {
+              wst = 0;
+              wpar ^= 1u;
             }
             // nothing issued later reads the slot of this CTA's own chunk 0
             if (half == 0 && s == 1 && i == 0) commit(c.bars + OFF_OWN0_FREE);
@@ -673,47 +646,34 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
               if (i == 1 && round == 0) RINGRNN_STAMP(g, 1);
 #endif
             }
-            auto stage_mmas = [&](int kh) -> bool {
-              int st;
-              if (resident) {
-                st = s * KC + i;
-                if (g == 0 && !mbar_wait(c.bars + OFF_W_FULL + 8 * st, 0, c.wctx, code + 3)) return false;
-              } else {
-                st = wst;
-#ifdef RINGRNN_TIMELINE
-                t0 = clock64();
-#endif
-                if (!mbar_wait(c.bars + OFF_W_FULL + 8 * st, wpar, c.wctx, code + 3)) return false;
-#ifdef RINGRNN_TIMELINE
-                acc_w += clock64() - t0;
-#endif
-              }
-              tcgen05_fence_after();
-              const uint32_t a_lo = desc_lo(c.a_base + slot * CHUNK_BYTES, 16) + 2 * (C_::KT / 16) * kh,
-                             b_lo = desc_lo(c.w_base + st * C_::WT_BYTES, 16);
-#pragma unroll
-              for (int ks = 0; ks < C_::KT / 16; ++ks) {
-                const uint32_t accum = (round > 0 || i > 0 || kh > 0 || ks > 0) ? 1u : 0u;
-                if (PAIR) umma_ss_pair_lo(c.tmem_base + acc * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc, accum);
-                else if constexpr (C_::HALFK)
-                  umma_ss_lo2(c.tmem_base + acc * 256, a_lo + 2 * ks, DESC_HI_SW128, b_lo + 2 * ks, B_HI, idesc, accum);
-                else umma_ss_lo(c.tmem_base + acc * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc, accum);
-              }
-              if (!resident) {
-                commit(c.bars + OFF_W_EMPTY + 8 * st);
-                if (++wst == NS) {
-                  wst = 0;
-                  wpar ^= 1u;
-                }
-              }
-              return true;
-            };
-            if constexpr (C_::KH == 1) {
-              if (!stage_mmas(0)) return;
+            int st;
+            if (resident) {
+              st = s * KC + i;
+              if (g == 0 && !mbar_wait(c.bars + OFF_W_FULL + 8 * st, 0, c.wctx, code + 3)) return;
             } else {
-#pragma unroll 1
-              for (int kh = 0; kh < C_::KH; ++kh)
-                if (!stage_mmas(kh)) return;
+              st = wst;
+#ifdef RINGRNN_TIMELINE
+              t0 = clock64();
+#endif
+              if (!mbar_wait(c.bars + OFF_W_FULL + 8 * st, wpar, c.wctx, code + 3)) return;
+#ifdef RINGRNN_TIMELINE
+              acc_w += clock64() - t0;
+#endif
+            }
+            tcgen05_fence_after();
+            const uint32_t a_lo = desc_lo(c.a_base + slot * CHUNK_BYTES, 16), b_lo = desc_lo(c.w_base + st * C_::WT_BYTES, 16);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              const uint32_t accum = (round > 0 || i > 0 || ks > 0) ? 1u : 0u;
+              if (PAIR) umma_ss_pair_lo(c.tmem_base + acc * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc, accum);
+              else umma_ss_lo(c.tmem_base + acc * 256, a_lo + 2 * ks, b_lo + 2 * ks, idesc, accum);
+            }
+            if (!resident) {
+              commit(c.bars + OFF_W_EMPTY + 8 * st);
+              if (++wst == NS) {
+                wst = 0;
+                wpar ^= 1u;
+              }
             }
             // early publication: the passes start at this CTA's own chunks, so after the first tile of the last pass
             // nothing issued later reads the slot of own chunk 0: the epilogue may overwrite it once these complete
@@ -765,7 +725,7 @@ __device__ __forceinline__ void relay_loop(const Ctx<NP, PAIR>& c, uint32_t tota
   for (uint32_t g = 0; g < total_steps; ++g) {
     for (int round = 0; round < R; ++round, ++ph) {
       if (t == 0) tile_start(it, round);
-      if (ACKS && (!FWD || t != 0)) {  // (ACKS: the kernel's own early-publication flag)
+      if (ACKS && (!FWD || t != 0)) {  // (ACKS: the kernel's own early-publication flag)  // (early_acks: the kernel's own EARLY flag)
         // early publication: chunk 0 of every peer reached this CTA as a copy out of the peer's own A slot; tell the
         // peer once it has landed, so that the peer knows when it may overwrite that slot again
         for (int q2 = 0; q2 < C_::C; ++q2)
@@ -1039,17 +999,6 @@ __device__ __forceinline__ void store_rows_via_smem(uint32_t stage, int lane, co
 }
 
 }  // namespace tcr
-
-// k-columns of one weight stage for a padded size and cluster shape (the weight tensor map's box must match)
-inline int weight_stage_cols(int NP, bool pair) {
-  if (pair) return 64;
-  switch (NP) {
-    case 128: return tcr::Cfg<128, false>::KT;
-    case 256: return tcr::Cfg<256, false>::KT;
-    case 512: return tcr::Cfg<512, false>::KT;
-    default: return tcr::Cfg<1024, false>::KT;
-  }
-}
 
 // How many clusters to launch: one per tile, but never more than can be resident at once (a second wave would
 // double the time of these persistent kernels; with fewer clusters the tiles are taken round-robin instead).
