@@ -77,6 +77,12 @@ FWD_SHAPES = [
     (64, 19200, 9, 2, "tanh", False),
     (512, 4352, 3, 2, "tanh", False),
     (1024, 2048, 3, 2, "silu", False),
+    # early publication of chunk 0 (N = 256 / 512) at its edges: a single step (nothing is ever sent), two steps (one
+    # send per tile), several tiles per cluster so that the send counters and barrier phases cross tile boundaries
+    (512, 4400, 1, 2, "tanh", False),
+    (512, 4400, 2, 2, "relu", False),
+    (256, 10240, 2, 2, "gelu", False),
+    (256, 300, 1, 2, "silu", False),
     # (relu is covered by the shapes above and by the benchmark-like cases below; with zero-mean random states many
     # pre-activations sit within bf16 rounding of relu's kink, where F' jumps between 0 and 1, so gradients of a
     # long random case differ from fp32 by a few percent in ANY bf16 implementation -- not a parity defect)
