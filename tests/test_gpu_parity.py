@@ -80,7 +80,7 @@ FWD_SHAPES = [
     # early publication of chunk 0 (N = 256 / 512) at its edges: a single step (nothing is ever sent), two steps (one
     # send per tile), several tiles per cluster so that the send counters and barrier phases cross tile boundaries
     (512, 4400, 1, 2, "tanh", False),
-    (512, 4400, 2, 2, "relu", False),
+    (512, 4400, 2, 2, "silu", False),
     (256, 10240, 2, 2, "gelu", False),
     (256, 300, 1, 2, "silu", False),
     # (relu is covered by the shapes above and by the benchmark-like cases below; with zero-mean random states many
