@@ -10,8 +10,8 @@ reference's pure-PyTorch twin of the same model (train/train_general_ring_no_gai
 both models starting from the same weights and seeing the same batches.
 
 Where the reference lives: $RINGRNN_REFERENCE_DIR, else baseline/_ref under the repository root (git-ignored; the build
-step copies the reference there when it is available), else /root/reference.  Skipped, with that reason, if none holds
-the script.
+step copies the reference's Python sources there when a checkout is available).  Skipped, with that reason, if neither
+holds the script.
 """
 import importlib
 import os
@@ -27,7 +27,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _reference_dir():
-    for d in (os.environ.get("RINGRNN_REFERENCE_DIR"), os.path.join(ROOT, "baseline", "_ref"), "/root/reference"):
+    for d in (os.environ.get("RINGRNN_REFERENCE_DIR"), os.path.join(ROOT, "baseline", "_ref")):
         if d and os.path.isfile(os.path.join(d, "train_general_ring_no_gain.py")):
             return d
     return None
@@ -37,8 +37,7 @@ def _reference_dir():
 def reference_modules():
     ref = _reference_dir()
     if ref is None:
-        pytest.skip("no copy of the reference (train_general_ring_no_gain.py) in $RINGRNN_REFERENCE_DIR, baseline/_ref "
-                    "or /root/reference")
+        pytest.skip("no copy of the reference (train_general_ring_no_gain.py) in $RINGRNN_REFERENCE_DIR or baseline/_ref")
     saved_path, saved_mods = list(sys.path), set(sys.modules)
     try:
         import matplotlib.pyplot  # noqa: F401
