@@ -152,8 +152,8 @@ def test_operator_refuses_cpu_tensors_loudly():
 
 
 def test_documented_binding_matches_the_real_struct():
-    """INTEGRATION.md prints the ctypes Problem structure a maintainer would paste into the reference: its field list must
-    be the one the library is built with (a short structure hands check_problem garbage)."""
+    """The integration guide prints the ctypes Problem structure a maintainer would paste into the reference: its field
+    list must be the one the library is built with (a short structure hands check_problem garbage)."""
     text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
     block = text[text.index("class Problem(C.Structure)"):]
     block = block[:block.index("def fwd(")]
