@@ -59,6 +59,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       relay_loop<NP, PAIR, false, EARLY>(c, total_steps, T, 320, [](int, int) {});
     } else if (warp == 3) {
       if constexpr (EARLY) sender_loop<NP, PAIR, false>(c, total_steps, T, 330, &tmDL, p.BP, cluster_id, n_clusters);
+      else if constexpr (C_::PULL) puller_loop<NP, PAIR, false>(c, total_steps, T, 330, &tmDL, p.BP, cluster_id, n_clusters);
     }
   } else {
     reg_inc<HIGH_REGS>();
@@ -75,6 +76,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     FreePhases<NP, PAIR> freed;
     uint32_t g = 0;
     uint32_t n_sent = 0, sent_waited = 0;  // early publication: sends of own chunk 0 handed over / known complete
+    uint32_t n_pub = 0;                    // exchange through global memory: publications of this CTA
     bool stop = false;  // a wait of this CTA was abandoned (the status word says which): same value in all 256 threads
     for (int tile = cluster_id; tile < p.n_tiles && !stop; tile += n_clusters) {
       const int b = tile * C_::TILE_ROWS + c.half * 128 + row;
@@ -336,8 +338,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           }
         }
         // delta_t: A operand of this step everywhere, and column block 0 of DL row block t (TMA store from the chunks)
-        stop = publish_chunks<NP, PAIR>(c, packed, row, h, warp, lane, &tmDL, q * 128,
-                                        t * p.BP + tile * C_::TILE_ROWS + c.half * 128);
+        if constexpr (C_::PULL)  // straight from registers into DL; the CTAs of the cluster, this one too, fetch it from there
+          stop = publish_global<NP, PAIR>(c, packed, h, warp, lane,
+                                          p.DL + ((size_t)t * p.BP + b) * ((size_t)dl_blocks * NP) + q * 128, n_pub++);
+        else
+          stop = publish_chunks<NP, PAIR>(c, packed, row, h, warp, lane, &tmDL, q * 128,
+                                          t * p.BP + tile * C_::TILE_ROWS + c.half * 128);
         if (stop) return;
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 12);
         // off the critical path: [delta | L*delta | R*delta] for the weight-gradient GEMM.  The scaled copies are
@@ -385,7 +391,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       };
 
       prefetch(T - 1);
-      freed.before_publish(c, g, rq, 308);
+      if (!C_::PULL) freed.before_publish(c, g, rq, 308);
       if constexpr (EARLY) {
         uint32_t packed[32];
         produce_half(T - 1, 0, packed);
@@ -475,7 +481,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           if (warp == 4 && lane == 0) RINGRNN_STAMP(g, s == 0 ? 5 : 7);
           tcgen05_fence_after();
           if (s == 0) {
-            freed.early(c, g, 308);
+            if (!C_::PULL) freed.early(c, g, 308);
             uint32_t sraw;
             tmem_ld1(tmem_base + lane_base + SUM_COL, &sraw);  // sum_i delta_t[b,i]
             tmem_ld_wait();
@@ -547,8 +553,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           dp[(size_t)T * p.BP] = dAr;
         }
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 9);
-        if (t > 0) freed.before_publish(c, g + 1, rq, 308);
-        else freed.end_of_step(c, g, 308);
+        if (!C_::PULL) {  // (with the exchange through global memory nothing here waits for the peers' slots)
+          if (t > 0) freed.before_publish(c, g + 1, rq, 308);
+          else freed.end_of_step(c, g, 308);
+        }
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 10);
         if (t > 0) {
           if constexpr (EARLY) {

@@ -64,6 +64,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     } else if (warp == 3) {
       if constexpr (EARLY)
         sender_loop<NP, PAIR>(c, total_steps, T, 230, p.Rh != nullptr ? &tmR0 : nullptr, p.BP, cluster_id, n_clusters);
+      else if constexpr (C_::PULL) {
+        // without a saved state nothing is stored, and the chunks travel as copies between the CTAs as elsewhere
+        if (p.Rh != nullptr && T > 1) puller_loop<NP, PAIR, true>(c, total_steps, T, 230, &tmR0, p.BP, cluster_id, n_clusters);
+      }
     }
   } else {
     reg_inc<HIGH_REGS>();
@@ -81,6 +85,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     const bool padded = p.N != NP;  // some of the NP columns are padding
     const int rq = (2 * q) / C_::SLOTS;  // the K round this CTA's own chunks belong to
     FreePhases<NP, PAIR> freed;
+    // exchange through global memory (Cfg::PULL, training): the state is written from registers and flagged; nothing
+    // here waits for the peers' slots
+    const bool pull = C_::PULL && p.Rh != nullptr;
+    uint32_t n_pub = 0;
     uint32_t g = 0;
     uint32_t n_sent = 0, sent_waited = 0;  // early publication: copies of own chunk 0 sent / known to have arrived
     bool stop = false;  // a wait of this CTA was abandoned (the status word says which): same value in all 256 threads
@@ -117,12 +125,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             mbar_wait(bars + OFF_D_FULL + 8 * s, g & 1u, wctx, 207);
             if (warp == 4 && lane == 0) RINGRNN_STAMP(g, s == 0 ? 5 : 7);
             tcgen05_fence_after();
-            if (s == 0) freed.early(c, g, 208);
+            if (s == 0 && !pull) freed.early(c, g, 208);
             // Last step of a tile: nothing is published, and the next tile's first operand comes by TMA, so its MMAs
             // wait for nothing but this accumulator.  The step's "free" phases must be consumed BEFORE the accumulator
             // is handed back, or the barrier could complete another phase first and the parity wait below would
             // never return.  (They complete together with this accumulator, give or take the skew between the CTAs.)
-            if (s == 1 && t + 1 == T) freed.end_of_step(c, g, 208);
+            if (s == 1 && t + 1 == T && !pull) freed.end_of_step(c, g, 208);
             const uint32_t col = tmem_base + lane_base + s * 256 + 32 * h;
             if (s == 0) {
               uint32_t sraw;
@@ -284,7 +292,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         // the barriers is waited for, published or not, so that none is skipped); then publish r_t:
         // it becomes the A operand of step t+1 everywhere and, in training, row block t+1 of the saved state
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 9);
-        if (t + 1 < T) {
+        if (C_::PULL && pull) {
+          if (t + 1 < T) {
+            stop = publish_global<NP, PAIR>(c, packed, h, warp, lane,
+                                            p.Rh + ((size_t)(t + 1) * p.BP + b) * NP + q * 128, n_pub++);
+            if (stop) break;
+          }
+        } else if (t + 1 < T) {
           freed.before_publish(c, g + 1, rq, 208);
           if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 10);
           if constexpr (EARLY) {

@@ -121,6 +121,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// async-proxy accesses to any state space (TMA stores to / loads from global memory) against generic-proxy ones
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
 __device__ __forceinline__ void tcgen05_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }

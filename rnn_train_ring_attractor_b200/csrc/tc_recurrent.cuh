@@ -160,6 +160,20 @@ struct Cfg {
   // sub-slice 0 to its peers while it still works on sub-slice 1, so that half of the state exchange is hidden behind
   // the second half of the epilogue instead of standing between two steps.
   static constexpr bool EARLY = !PAIR && ROUNDS == 1 && C > 1;
+  // Exchange through global memory (two K rounds = clusters of 8), used whenever the published tensor is kept in
+  // global memory anyway (the saved state in training, delta for the weight gradients).  A chunk that goes to seven
+  // peers as seven distributed-shared-memory copies leaves its SM at about 10 B/clk (224 KB per step and CTA: 19-21 K
+  // cycles for an all-gather, measured), and the copies may only start once every peer has freed the slots.  Instead
+  // the epilogue threads write their part of the chunks straight from registers into that tensor (it replaces the TMA
+  // store), fence, and one of them raises a flag in every CTA of the cluster, its own included; a thread per slice in
+  // each CTA (puller_loop) loads the chunks into the A buffer with TMA as soon as ITS OWN MMAs have left the slots.
+  // Data enters an SM at the 50 B/clk of any TMA load, nothing waits for a cluster-wide "free", and the chunks of the
+  // second round -- known since the previous step's epilogue -- are in flight the moment the first round ends.
+#ifdef RINGRNN_NO_PULL
+  static constexpr bool PULL = false;
+#else
+  static constexpr bool PULL = ROUNDS > 1;
+#endif
   static_assert(NS >= 2, "weight ring too small");
   static_assert(NS <= 16, "barrier block sized for 16 stages");
   static_assert(WT_BYTES % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
@@ -184,6 +198,11 @@ constexpr uint32_t OFF_OWN0_FREE = 456;   // (early publication) this CTA's MMAs
 constexpr uint32_t OFF_SENT_DONE = 464;   // (early publication) the peers have received the copies of own chunk 0
 constexpr uint32_t OFF_STORE0_DONE = 472; // (early publication) the TMA store of own chunk 0 has finished reading its slot
 constexpr uint32_t OFF_UV = 512;       // float u[128], v[128]
+// Exchange through global memory.  Both kinds of barrier come in pairs used alternately (publication n, step g: member
+// n & 1, g & 1): a waiter can tell the current phase from the one before by parity, no further, and here a signaller may
+// be one publication (one step) ahead of a waiter, never two.
+constexpr uint32_t OFF_READY = 1536;   // [8][2] slice i's chunks are complete in global memory
+constexpr uint32_t OFF_LOCAL_FREE = 1664;  // [2][2] per round: THIS CTA's MMAs of the round are complete
 
 template <int REGS>
 __device__ __forceinline__ void reg_dec() {
@@ -404,6 +423,8 @@ __device__ __forceinline__ Ctx<NP, PAIR> setup_cta(uint8_t* smem_raw, const floa
     mbar_init(c.bars + OFF_OWN0_FREE, 1);
     mbar_init(c.bars + OFF_SENT_DONE, C_::C > 1 ? C_::C - 1 : 1);
     mbar_init(c.bars + OFF_STORE0_DONE, 1);
+    for (int i = 0; i < 16; ++i) mbar_init(c.bars + OFF_READY + 8 * i, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(c.bars + OFF_LOCAL_FREE + 8 * i, 1);
     fence_mbar_init();
   }
   if (threadIdx.x < 256) {
@@ -530,9 +551,10 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
   int wst = 0;          // ring stage of the next weight tile
   uint32_t wpar = 0;    // parity of that stage's current fill
   int t = 0;            // step within the tile
+  const bool pull = C_::PULL && stores;  // every chunk, this CTA's own included, arrives as a TMA load (puller_loop)
   if (!FWD && total_steps > 0)  // reverse: nothing loads the first A operand by TMA, peers push it
     for (int slot = 0; slot < SL; ++slot)
-      if ((slot >> 1) != c.q) mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * slot, CHUNK_BYTES);
+      if (pull || (slot >> 1) != c.q) mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * slot, CHUNK_BYTES);
   auto commit = [&](uint32_t bar) {
     if (PAIR) umma_commit_pair(bar, c.pair_mask);
     else umma_commit(bar);
@@ -638,7 +660,7 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
               acc_a += clock64() - t0;
               t0 = clock64();
 #endif
-              if (next_by_copy && ((next_round * SL + slot) >> 1) != c.q)
+              if (next_by_copy && (pull || ((next_round * SL + slot) >> 1) != c.q))
                 mbar_arrive_expect_tx(c.bars + OFF_A_FULL + 8 * slot, CHUNK_BYTES);
               if (PAIR && !mbar_wait<true>(c.bars + OFF_A_PAIR + 8 * slot, g & 1u, c.wctx, code + 2)) return;
 #ifdef RINGRNN_TIMELINE
@@ -685,13 +707,14 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
           }
         }
       }
-      if (R > 1 && round == rq && stores && (!FWD || t != 0)) {
+      if (R > 1 && round == rq && stores && !pull && (!FWD || t != 0)) {
         // this CTA's own chunks sit in slots a peer fills in the next phase: the TMA store that also reads them
         // must be through before "free" goes out
         if (!mbar_wait(c.bars + OFF_STORE_DONE, npub & 1u, c.wctx, code + 4)) return;
         ++npub;
       }
       commit(c.bars + OFF_MMA_DONE);
+      if (C_::PULL) commit(c.bars + OFF_LOCAL_FREE + 16 * round + 8 * (g & 1u));  // the pullers refill the slots behind this
       // "this MMA unit no longer reads the A buffer of this round", straight to every CTA of the cluster
       const uint32_t free_bar = c.bars + OFF_ALL_FREE + 8 * round;
       if (PAIR) umma_commit_pair(free_bar, (uint16_t)((1u << C_::CL) - 1u));
@@ -949,6 +972,81 @@ __device__ __forceinline__ void sender_loop(const Ctx<NP, PAIR>& c, uint32_t tot
     }
   }
   if (tm_store != nullptr && lane == 0) bulk_wait_all<0>();
+}
+
+// Exchange through global memory (Cfg::PULL).
+// Publisher: all 256 epilogue threads call publish_global with their 2 x 16 packed words; `row_ptr` points at the
+// thread's sample row, first column of the CTA's 128-column block, in the tensor that keeps the published values
+// (saved state, or the delta block of DL); `n_pub` counts this CTA's publications.  Returns `stop` as publish_chunks does.
+template <int NP, bool PAIR>
+__device__ __forceinline__ bool publish_global(const Ctx<NP, PAIR>& c, const uint32_t* packed, int h, int warp, int lane,
+                                               __nv_bfloat16* row_ptr, uint32_t n_pub) {
+  using C_ = Cfg<NP, PAIR>;
+  using namespace tc;
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    uint4* d = reinterpret_cast<uint4*>(row_ptr + 64 * s + 32 * h);
+#pragma unroll
+    for (int v = 0; v < 4; ++v)
+      d[v] = make_uint4(packed[s * 16 + 4 * v], packed[s * 16 + 4 * v + 1], packed[s * 16 + 4 * v + 2], packed[s * 16 + 4 * v + 3]);
+  }
+  __threadfence();  // this thread's rows are visible device-wide before the barrier below lets the flags go out
+  const bool stop = named_bar_or(1, 256, *c.wctx.dead != 0);
+  if (warp == 4 && lane == 0 && !stop) {
+    fence_proxy_async_all();  // the readers are TMA loads
+    for (int q2 = 0; q2 < C_::C; ++q2)
+      mbar_arrive_cluster(c.bars + OFF_READY + 16 * c.q + 8 * (n_pub & 1u), c.peer_rank(q2));
+  }
+  return stop;
+}
+
+// Consumer: all 32 threads of warp 3 run this; lane i < C fetches what slice i publishes (this CTA's own slice too).
+// It waits for this CTA's MMAs of the phase before the one the chunks belong to (they read what the slots hold
+// now), then for that slice's flag, then loads the two chunks with TMA; the loads complete the barriers the MMA thread
+// has armed.  `tmX` maps the tensor the publishers write; a step's operand is row block t (forward: the state
+// before step t; the first one of a tile is loaded by the relay thread) resp. T-1-t (reverse: delta of that step).
+// How far a flag can run ahead of its reader: slice i's publication n+2 follows MMAs that needed this CTA's publication
+// n+1, which follows this CTA's MMAs on the chunks of publication n -- so at most one ahead, which the paired barriers
+// tell apart.  Likewise the MMA thread is at most one step ahead of a lane (a forward tile's first step needs no lane).
+// Forward with T = 1 publishes nothing: the caller does not start this loop then.
+template <int NP, bool PAIR, bool FWD>
+__device__ __forceinline__ void puller_loop(const Ctx<NP, PAIR>& c, uint32_t total_steps, int T, int code,
+                                            const CUtensorMap* tmX, int BP, int cluster_id, int n_clusters) {
+  using C_ = Cfg<NP, PAIR>;
+  using namespace tc;
+  constexpr int R = C_::ROUNDS;
+  const int q2 = threadIdx.x & 31;
+  if (q2 >= C_::C) return;
+  const int round = (2 * q2) / C_::SLOTS;  // the K round slice q2's chunks belong to
+  static_assert(R == 2, "the slot hand-over below is written for two K rounds");
+  uint32_t n = 0;  // publications of slice q2 fetched so far
+  int t = 0, it = 0;
+  for (uint32_t g = 0; g < total_steps; ++g) {
+    // The slots hold the chunks of the phase before: round 0 of this step (for a slice of round 1) or round 1 of the
+    // previous step (for a slice of round 0).  One phase of that round's barrier per step, consumed every step,
+    // whether a load follows or not, so that the parity never slips.
+    if (round == 1) {
+      if (!mbar_wait(c.bars + OFF_LOCAL_FREE + 8 * (g & 1u), (g >> 1) & 1u, c.wctx, code + 1)) return;
+    } else if (g > 0) {
+      if (!mbar_wait(c.bars + OFF_LOCAL_FREE + 16 + 8 * ((g - 1) & 1u), ((g - 1) >> 1) & 1u, c.wctx, code + 1)) return;
+    }
+    if (!FWD || t != 0) {
+      if (!mbar_wait<true>(c.bars + OFF_READY + 16 * q2 + 8 * (n & 1u), (n >> 1) & 1u, c.wctx, code)) return;
+      ++n;
+      fence_proxy_async_all();
+      const int tile = cluster_id + it * n_clusters;
+      const int y = (FWD ? t : T - 1 - t) * BP + tile * C_::TILE_ROWS + c.half * 128;
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        const int slot = (2 * q2 + s) % C_::SLOTS;
+        tma_load_2d(c.a_base + slot * CHUNK_BYTES, tmX, c.bars + OFF_A_FULL + 8 * slot, q2 * 128 + 64 * s, y);
+      }
+    }
+    if (++t == T) {
+      t = 0;
+      ++it;
+    }
+  }
 }
 
 // ---- epilogue global-memory traffic ---------------------------------------------------------------------------
