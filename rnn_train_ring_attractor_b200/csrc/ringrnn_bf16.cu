@@ -112,7 +112,9 @@ Layout layout_of(const RingRnnProblem& p) {
   l.RB = block_rows(l.pair);
   l.tile_rows = l.pair ? 256 : 128;
   l.w_bytes = align_up((size_t)l.C * 2 * l.ng * l.RB * l.NP * 2, 1024);
-  l.r0_bytes = align_up((size_t)l.BP * l.NP * 2, 1024);
+  // initial state in bf16; with two K rounds (N > 512) two more row blocks through which the CTAs of a cluster
+  // exchange the state when none is saved (TcFwdParams::X)
+  l.r0_bytes = align_up((size_t)l.BP * l.NP * 2 * (l.NP > 512 ? 3 : 1), 1024);
   l.dec_bytes = align_up((size_t)2 * l.C * 3 * p.T * l.BP * 4, 1024);
   l.state_bytes = align_up((size_t)l.BP * l.NP * 2, 1024);  // one time slot of Rh / Dh
   return l;
@@ -202,7 +204,8 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   if (!make_tmap_bf16_2d(&tmW, Wf, (uint64_t)l.C * 2 * l.ng * l.RB, (uint64_t)l.NP, l.pair ? l.RB / 2 : l.RB, 64))
     return RINGRNN_ERR_CUDA;
   // one map serves the initial-state loads (rows [0, BP)) and, in training, the saved-state stores (rows up to T*BP)
-  if (!make_tmap_bf16_2d(&tmR0, R0, (uint64_t)(keep_all ? p.T + 1 : 1) * l.BP, (uint64_t)l.NP, 128, 64))
+  const bool two_rounds = l.NP > 512;
+  if (!make_tmap_bf16_2d(&tmR0, R0, (uint64_t)(keep_all ? p.T + 1 : (two_rounds ? 3 : 1)) * l.BP, (uint64_t)l.NP, 128, 64))
     return RINGRNN_ERR_CUDA;
 
   const bool want_dec = a.dec_x || a.dec_y || a.dec_ta;
@@ -217,6 +220,8 @@ int bf16_forward(const RingRnnFwdArgs& a, const DevProblem& dp, cudaStream_t s) 
   fp.J0 = p.J0; fp.J1 = p.J1; fp.alpha = p.alpha;
   fp.A = p.A; fp.r_init = p.r_init;
   fp.Rh = Rh; fp.Dh = Dh; fp.Sg = Sg;
+  fp.X = two_rounds ? R0 : nullptr;  // (= Rh when every step is kept)
+  fp.x_ring = keep_all ? 0 : 1;
   fp.hist = a.bump_history;
   fp.dec_part = want_dec ? dec_part : nullptr;
   fp.dec_u = a.dec_u; fp.dec_v = a.dec_v;
@@ -410,6 +415,8 @@ int bf16_backward_ckpt(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream
     fp.J0 = p.J0; fp.J1 = p.J1; fp.alpha = p.alpha;
     fp.A = p.A; fp.r_init = state0;
     fp.Rh = Rh; fp.Dh = Dh; fp.Sg = Sg;
+    fp.X = l.NP > 512 ? Rh : nullptr;
+    fp.x_ring = 0;
     fp.status = status;
     fp.t0 = t0; fp.T_total = p.T;
     int rc = tc_forward_launch(p.activation, l.NP, l.pair, tmWf, tmR0, fp, s);

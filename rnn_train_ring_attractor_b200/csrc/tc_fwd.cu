@@ -48,7 +48,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       producer_loop<NP, PAIR, GEN, EARLY>(c, &tmW, total_steps, 202, ng);
 #endif
     } else if (warp == 1 && lane == 0) {
-      if (c.leader) mma_loop<NP, PAIR, true, GEN>(c, total_steps, T, 210, p.Rh != nullptr, ng);
+      if (c.leader) mma_loop<NP, PAIR, true, GEN>(c, total_steps, T, 210, p.Rh != nullptr || (C_::PULL && p.X != nullptr), ng);
     } else if (warp == 2 && lane == 0) {
       tma_prefetch_desc(&tmR0);
       relay_loop<NP, PAIR, true, EARLY>(c, total_steps, T, 220, [&](int it, int round) {
@@ -65,8 +65,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       if constexpr (EARLY)
         sender_loop<NP, PAIR>(c, total_steps, T, 230, p.Rh != nullptr ? &tmR0 : nullptr, p.BP, cluster_id, n_clusters);
       else if constexpr (C_::PULL) {
-        // without a saved state nothing is stored, and the chunks travel as copies between the CTAs as elsewhere
-        if (p.Rh != nullptr && T > 1) puller_loop<NP, PAIR, true>(c, total_steps, T, 230, &tmR0, p.BP, cluster_id, n_clusters);
+        if (p.X != nullptr && T > 1)
+          puller_loop<NP, PAIR, true>(c, total_steps, T, 230, &tmR0, p.BP, cluster_id, n_clusters, p.x_ring != 0);
       }
     }
   } else {
@@ -85,9 +85,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     const bool padded = p.N != NP;  // some of the NP columns are padding
     const int rq = (2 * q) / C_::SLOTS;  // the K round this CTA's own chunks belong to
     FreePhases<NP, PAIR> freed;
-    // exchange through global memory (Cfg::PULL, training): the state is written from registers and flagged; nothing
-    // here waits for the peers' slots
-    const bool pull = C_::PULL && p.Rh != nullptr;
+    // exchange through global memory (Cfg::PULL): the state is written from registers and flagged; nothing here waits
+    // for the peers' slots
+    const bool pull = C_::PULL && p.X != nullptr;
     uint32_t n_pub = 0;
     uint32_t g = 0;
     uint32_t n_sent = 0, sent_waited = 0;  // early publication: copies of own chunk 0 sent / known to have arrived
@@ -294,8 +294,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 9);
         if (C_::PULL && pull) {
           if (t + 1 < T) {
-            stop = publish_global<NP, PAIR>(c, packed, h, warp, lane,
-                                            p.Rh + ((size_t)(t + 1) * p.BP + b) * NP + q * 128, n_pub++);
+            const int rb = p.x_ring ? 1 + ((t + 1) & 1) : t + 1;
+            stop = publish_global<NP, PAIR>(c, packed, h, warp, lane, p.X + ((size_t)rb * p.BP + b) * NP + q * 128, n_pub++);
             if (stop) break;
           }
         } else if (t + 1 < T) {

@@ -82,6 +82,12 @@ struct TcFwdParams {
   int t0, T_total;
   float* ckpt;           // [ceil(T/ckpt_every)][B][N] fp32: slot c receives the state after step c*ckpt_every - 1
   int ckpt_every;        //   (slot 0, the initial state, is the caller's); nullptr = none
+  // Two K rounds (N > 512): the CTAs of a cluster exchange the state through global memory.  X = Rh when the state is
+  // saved (step t reads row block t, writes t+1); otherwise X = the initial-state buffer extended to three row blocks,
+  // blocks 1 and 2 used in turn (x_ring = 1: step t reads block 1 + (t & 1), writes 1 + ((t+1) & 1)).  The tensor map
+  // of the initial state covers X.
+  __nv_bfloat16* X;
+  int x_ring;
 };
 
 struct TcBwdParams {
@@ -1004,14 +1010,16 @@ __device__ __forceinline__ bool publish_global(const Ctx<NP, PAIR>& c, const uin
 // It waits for this CTA's MMAs of the phase before the one the chunks belong to (they read what the slots hold
 // now), then for that slice's flag, then loads the two chunks with TMA; the loads complete the barriers the MMA thread
 // has armed.  `tmX` maps the tensor the publishers write; a step's operand is row block t (forward: the state
-// before step t; the first one of a tile is loaded by the relay thread) resp. T-1-t (reverse: delta of that step).
+// before step t; the first one of a tile is loaded by the relay thread; `ring`: block 1 + (t & 1) of a three-block
+// buffer when no state is saved) resp. T-1-t (reverse: delta of that step).
 // How far a flag can run ahead of its reader: slice i's publication n+2 follows MMAs that needed this CTA's publication
 // n+1, which follows this CTA's MMAs on the chunks of publication n -- so at most one ahead, which the paired barriers
 // tell apart.  Likewise the MMA thread is at most one step ahead of a lane (a forward tile's first step needs no lane).
 // Forward with T = 1 publishes nothing: the caller does not start this loop then.
 template <int NP, bool PAIR, bool FWD>
 __device__ __forceinline__ void puller_loop(const Ctx<NP, PAIR>& c, uint32_t total_steps, int T, int code,
-                                            const CUtensorMap* tmX, int BP, int cluster_id, int n_clusters) {
+                                            const CUtensorMap* tmX, int BP, int cluster_id, int n_clusters,
+                                            bool ring = false) {
   using C_ = Cfg<NP, PAIR>;
   using namespace tc;
   constexpr int R = C_::ROUNDS;
@@ -1035,7 +1043,8 @@ __device__ __forceinline__ void puller_loop(const Ctx<NP, PAIR>& c, uint32_t tot
       ++n;
       fence_proxy_async_all();
       const int tile = cluster_id + it * n_clusters;
-      const int y = (FWD ? t : T - 1 - t) * BP + tile * C_::TILE_ROWS + c.half * 128;
+      const int rb = FWD ? (ring ? 1 + (t & 1) : t) : T - 1 - t;
+      const int y = rb * BP + tile * C_::TILE_ROWS + c.half * 128;
 #pragma unroll
       for (int s = 0; s < 2; ++s) {
         const int slot = (2 * q2 + s) % C_::SLOTS;

@@ -280,6 +280,31 @@ def test_fused_python_surface_and_rollout():
     assert torch.allclose(final2, final)
 
 
+@pytest.mark.parametrize("N,B,T", [(1024, 130, 9), (640, 300, 6), (1024, 260, 2), (1024, 64, 1)])
+def test_two_round_rollout_matches_the_training_forward(N, B, T, achieved):
+    """N > 512 (two K rounds): the CTAs of a cluster exchange the state through global memory -- through the saved
+    state in training, through a three-block ring when nothing is saved.  Both forwards must decode the same angles
+    and end in the same state, and agree with the oracle within the bf16-mode tolerance."""
+    from rnn_train_ring_attractor_b200.fused import ring_rnn_fused, ring_rnn_rollout
+    case = orc.make_case(N, B, T, "tanh", seed=11)
+    case.J0 = -0.1
+    ref_loss, _, _, ref_hist = orc.train_step_ref(case, lean=True)
+    A, r0, tgt = _dev(case.A, case.r_init, case.target)
+    Wa = case.Wa.cuda().requires_grad_(True)
+    Wo = case.Wo.cuda().requires_grad_(True)
+    loss, parts, decoded, final = ring_rnn_fused(A, Wa, case.J0, case.J1, Wo, r0, case.alpha, "tanh", tgt,
+                                                 precision="bf16")
+    dec2, final2 = ring_rnn_rollout(A, Wa.detach(), case.J0, case.J1, Wo.detach(), r0, case.alpha, "tanh",
+                                    precision="bf16")
+    e_final = orc.rel_err(final2, final)
+    e_dec = float(orc.angular_error(dec2.cpu(), decoded.detach().cpu()).max())
+    e_ref = orc.rel_err(final2, ref_hist[-1])
+    achieved(f"two-round rollout N{N}-B{B}-T{T} bf16", rollout_vs_training_final=e_final, rollout_vs_training_decode=e_dec,
+             final_vs_oracle=e_ref)
+    assert e_final < 1e-6 and e_dec < 1e-6  # the same arithmetic in the same order
+    assert e_ref < 1e-2
+
+
 def test_reference_style_model_trains_on_the_operator():
     """A model written the way the reference's GeneralizedRingAttractorNoGain.forward is
     (train_general_ring_no_gain.py:78-118): star-import, float J0/J1, alpha=0.15, zero-padded 16 action
