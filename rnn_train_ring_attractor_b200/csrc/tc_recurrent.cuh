@@ -996,12 +996,14 @@ __device__ __forceinline__ bool publish_global(const Ctx<NP, PAIR>& c, const uin
     for (int v = 0; v < 4; ++v)
       d[v] = make_uint4(packed[s * 16 + 4 * v], packed[s * 16 + 4 * v + 1], packed[s * 16 + 4 * v + 2], packed[s * 16 + 4 * v + 3]);
   }
-  __threadfence();  // this thread's rows are visible device-wide before the barrier below lets the flags go out
+  // The barrier orders the 256 threads' stores before the one fence below, whose release is cumulative over them (the
+  // pattern of a grid-wide barrier: sync the block, then one thread fences and signals).
   const bool stop = named_bar_or(1, 256, *c.wctx.dead != 0);
   if (warp == 4 && lane == 0 && !stop) {
+    __threadfence();          // the release for all the signals below
     fence_proxy_async_all();  // the readers are TMA loads
     for (int q2 = 0; q2 < C_::C; ++q2)
-      mbar_arrive_cluster(c.bars + OFF_READY + 16 * c.q + 8 * (n_pub & 1u), c.peer_rank(q2));
+      mbar_arrive_cluster_relaxed(c.bars + OFF_READY + 16 * c.q + 8 * (n_pub & 1u), c.peer_rank(q2));
   }
   return stop;
 }
