@@ -208,7 +208,7 @@ constexpr uint32_t OFF_UV = 512;       // float u[128], v[128]
 // n & 1, g & 1): a waiter can tell the current phase from the one before by parity, no further, and here a signaller may
 // be one publication (one step) ahead of a waiter, never two.
 constexpr uint32_t OFF_READY = 1536;   // [8][2] slice i's chunks are complete in global memory
-constexpr uint32_t OFF_LOCAL_FREE = 1664;  // [2][2] per round: THIS CTA's MMAs of the round are complete
+constexpr uint32_t OFF_PAIR_FREE = 1664;  // [2 rounds][4 slot pairs][2] THIS CTA's MMAs of the round no longer read slots 2i, 2i+1
 
 template <int REGS>
 __device__ __forceinline__ void reg_dec() {
@@ -430,7 +430,7 @@ __device__ __forceinline__ Ctx<NP, PAIR> setup_cta(uint8_t* smem_raw, const floa
     mbar_init(c.bars + OFF_SENT_DONE, C_::C > 1 ? C_::C - 1 : 1);
     mbar_init(c.bars + OFF_STORE0_DONE, 1);
     for (int i = 0; i < 16; ++i) mbar_init(c.bars + OFF_READY + 8 * i, 1);
-    for (int i = 0; i < 4; ++i) mbar_init(c.bars + OFF_LOCAL_FREE + 8 * i, 1);
+    for (int i = 0; i < 16; ++i) mbar_init(c.bars + OFF_PAIR_FREE + 8 * i, 1);
     fence_mbar_init();
   }
   if (threadIdx.x < 256) {
@@ -703,6 +703,10 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
                 wpar ^= 1u;
               }
             }
+            // exchange through global memory: the second pass is the last reader of a slot; a pair of slots (one
+            // slice's two chunks) is handed to its puller as soon as the pass is past it
+            if (C_::PULL && s == 1 && (slot & 1))
+              commit(c.bars + OFF_PAIR_FREE + 64 * round + 16 * (slot >> 1) + 8 * (g & 1u));
             // early publication: the passes start at this CTA's own chunks, so after the first tile of the last pass
             // nothing issued later reads the slot of own chunk 0: the epilogue may overwrite it once these complete
             if (EARLY_ANY && s == 1 && grp == ng - 1 && i == 0) commit(c.bars + OFF_OWN0_FREE);
@@ -720,7 +724,6 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
         ++npub;
       }
       commit(c.bars + OFF_MMA_DONE);
-      if (C_::PULL) commit(c.bars + OFF_LOCAL_FREE + 16 * round + 8 * (g & 1u));  // the pullers refill the slots behind this
       // "this MMA unit no longer reads the A buffer of this round", straight to every CTA of the cluster
       const uint32_t free_bar = c.bars + OFF_ALL_FREE + 8 * round;
       if (PAIR) umma_commit_pair(free_bar, (uint16_t)((1u << C_::CL) - 1u));
@@ -1032,13 +1035,14 @@ __device__ __forceinline__ void puller_loop(const Ctx<NP, PAIR>& c, uint32_t tot
   uint32_t n = 0;  // publications of slice q2 fetched so far
   int t = 0, it = 0;
   for (uint32_t g = 0; g < total_steps; ++g) {
-    // The slots hold the chunks of the phase before: round 0 of this step (for a slice of round 1) or round 1 of the
-    // previous step (for a slice of round 0).  One phase of that round's barrier per step, consumed every step,
-    // whether a load follows or not, so that the parity never slips.
+    // The two slots hold chunks of the phase before: round 0 of this step (for a slice of round 1) or round 1 of the
+    // previous step (for a slice of round 0).  One phase of that barrier per step, consumed every step, whether a
+    // load follows or not, so that the parity never slips.
+    const uint32_t pair_free = c.bars + OFF_PAIR_FREE + 16 * (q2 % (C_::SLOTS / 2));
     if (round == 1) {
-      if (!mbar_wait(c.bars + OFF_LOCAL_FREE + 8 * (g & 1u), (g >> 1) & 1u, c.wctx, code + 1)) return;
+      if (!mbar_wait(pair_free + 8 * (g & 1u), (g >> 1) & 1u, c.wctx, code + 1)) return;
     } else if (g > 0) {
-      if (!mbar_wait(c.bars + OFF_LOCAL_FREE + 16 + 8 * ((g - 1) & 1u), ((g - 1) >> 1) & 1u, c.wctx, code + 1)) return;
+      if (!mbar_wait(pair_free + 64 + 8 * ((g - 1) & 1u), ((g - 1) >> 1) & 1u, c.wctx, code + 1)) return;
     }
     if (!FWD || t != 0) {
       if (!mbar_wait<true>(c.bars + OFF_READY + 16 * q2 + 8 * (n & 1u), (n >> 1) & 1u, c.wctx, code)) return;
