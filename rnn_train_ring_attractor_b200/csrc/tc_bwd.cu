@@ -340,7 +340,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         // delta_t: A operand of this step everywhere, and column block 0 of DL row block t (TMA store from the chunks)
         if constexpr (C_::PULL)  // straight from registers into DL; the CTAs of the cluster, this one too, fetch it from there
           stop = publish_global<NP, PAIR>(c, packed, h, warp, lane,
-                                          p.DL + ((size_t)t * p.BP + b) * ((size_t)dl_blocks * NP) + q * 128, n_pub++);
+                                          p.DL + ((size_t)t * p.BP + b) * ((size_t)dl_blocks * NP) + q * 128,
+                                          (size_t)dl_blocks * NP, n_pub++);
         else
           stop = publish_chunks<NP, PAIR>(c, packed, row, h, warp, lane, &tmDL, q * 128,
                                           t * p.BP + tile * C_::TILE_ROWS + c.half * 128);

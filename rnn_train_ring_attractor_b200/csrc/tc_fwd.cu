@@ -295,7 +295,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (C_::PULL && pull) {
           if (t + 1 < T) {
             const int rb = p.x_ring ? 1 + ((t + 1) & 1) : t + 1;
-            stop = publish_global<NP, PAIR>(c, packed, h, warp, lane, p.X + ((size_t)rb * p.BP + b) * NP + q * 128, n_pub++);
+            stop = publish_global<NP, PAIR>(c, packed, h, warp, lane, p.X + ((size_t)rb * p.BP + b) * NP + q * 128, (size_t)NP,
+                                            n_pub++);
             if (stop) break;
           }
         } else if (t + 1 < T) {

@@ -986,27 +986,35 @@ __device__ __forceinline__ void sender_loop(const Ctx<NP, PAIR>& c, uint32_t tot
 // Exchange through global memory (Cfg::PULL).
 // Publisher: all 256 epilogue threads call publish_global with their 2 x 16 packed words; `row_ptr` points at the
 // thread's sample row, first column of the CTA's 128-column block, in the tensor that keeps the published values
-// (saved state, or the delta block of DL); `n_pub` counts this CTA's publications.  Returns `stop` as publish_chunks does.
+// (saved state, or the delta block of DL), whose rows are `row_stride` elements apart; `n_pub` counts this CTA's
+// publications.  Returns `stop` as publish_chunks does.
+template <bool STREAM = true>
+__device__ __forceinline__ void store_rows_via_smem(uint32_t stage, int lane, const uint32_t* w16, uint8_t* dst_row0,
+                                                    size_t row_stride_bytes);
+
 template <int NP, bool PAIR>
 __device__ __forceinline__ bool publish_global(const Ctx<NP, PAIR>& c, const uint32_t* packed, int h, int warp, int lane,
-                                               __nv_bfloat16* row_ptr, uint32_t n_pub) {
+                                               __nv_bfloat16* row_ptr, size_t row_stride, uint32_t n_pub) {
   using C_ = Cfg<NP, PAIR>;
   using namespace tc;
+  // through the warp's transposition buffer: a store instruction then covers 8 rows x 64 bytes instead of 32 rows x
+  // 16 bytes (the direct form kept the load/store unit busy for 1.3-2.8 K cycles per publication)
+  const uint32_t stage = c.stage_base + (uint32_t)(warp - 4) * 2048u;
 #pragma unroll
-  for (int s = 0; s < 2; ++s) {
-    uint4* d = reinterpret_cast<uint4*>(row_ptr + 64 * s + 32 * h);
-#pragma unroll
-    for (int v = 0; v < 4; ++v)
-      d[v] = make_uint4(packed[s * 16 + 4 * v], packed[s * 16 + 4 * v + 1], packed[s * 16 + 4 * v + 2], packed[s * 16 + 4 * v + 3]);
-  }
+  for (int s = 0; s < 2; ++s)
+    store_rows_via_smem<false>(stage, lane, packed + 16 * s,
+                               reinterpret_cast<uint8_t*>(row_ptr - (size_t)lane * row_stride + 64 * s + 32 * h), row_stride * 2);
   // The barrier orders the 256 threads' stores before the one fence below, whose release is cumulative over them (the
   // pattern of a grid-wide barrier: sync the block, then one thread fences and signals).
   const bool stop = named_bar_or(1, 256, *c.wctx.dead != 0);
-  if (warp == 4 && lane == 0 && !stop) {
-    __threadfence();          // the release for all the signals below
-    fence_proxy_async_all();  // the readers are TMA loads
-    for (int q2 = 0; q2 < C_::C; ++q2)
-      mbar_arrive_cluster_relaxed(c.bars + OFF_READY + 16 * c.q + 8 * (n_pub & 1u), c.peer_rank(q2));
+  if (warp == 4 && !stop) {
+    if (lane == 0) {
+      __threadfence();          // the release for all the signals below
+      fence_proxy_async_all();  // the readers are TMA loads
+    }
+    __syncwarp();  // the fence precedes the other lanes' signals
+    if (lane < C_::C)  // one signal per lane: in turn they took 1 K cycles
+      mbar_arrive_cluster_relaxed(c.bars + OFF_READY + 16 * c.q + 8 * (n_pub & 1u), c.peer_rank(lane));
   }
   return stop;
 }
@@ -1088,6 +1096,7 @@ __device__ __forceinline__ void load_blocked(const __nv_bfloat16* base, int lane
 }
 // The warp's 32 rows x 64 bytes (lane = row, w16 = its 16 words) to row-major global memory: `dst_row0` points at
 // row 0 of the warp's block, consecutive rows are `row_stride_bytes` apart; `stage` is the warp's 2 KB buffer.
+template <bool STREAM>
 __device__ __forceinline__ void store_rows_via_smem(uint32_t stage, int lane, const uint32_t* w16, uint8_t* dst_row0,
                                                     size_t row_stride_bytes) {
   const uint32_t sw = ((uint32_t)lane >> 1) & 3u;
@@ -1106,7 +1115,9 @@ __device__ __forceinline__ void store_rows_via_smem(uint32_t stage, int lane, co
     const uint32_t addr = stage + r * 64 + ((piece ^ (((uint32_t)r >> 1) & 3u)) << 4);
     uint32_t a, b, c2, d;
     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c2), "=r"(d) : "r"(addr));
-    tc::st_cs_v4(dst_row0 + (size_t)r * row_stride_bytes + piece * 16, a, b, c2, d);
+    uint8_t* dst = dst_row0 + (size_t)r * row_stride_bytes + piece * 16;
+    if (STREAM) tc::st_cs_v4(dst, a, b, c2, d);
+    else *reinterpret_cast<uint4*>(dst) = make_uint4(a, b, c2, d);
   }
   __syncwarp();
 }
