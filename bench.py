@@ -343,7 +343,9 @@ def run_timeline(args, wl):
         steps = []
         for g in (20, 21, 22, 40):
             base = buf[g * 16]
-            row = {n: int(buf[g * 16 + i] - base) for i, n in enumerate(names[kernel])}
+            # a point the kernel variant does not pass leaves its slot unstamped
+            row = {n: (int(buf[g * 16 + i] - base) if 0 <= buf[g * 16 + i] - base < 10 ** 9 else None)
+                   for i, n in enumerate(names[kernel])}
             row.update(step=g, next_step_start=int(buf[(g + 1) * 16] - base), WAIT_W=int(buf[g * 16 + 13]), WAIT_A=int(buf[g * 16 + 14]))
             steps.append(row)
         out[kernel] = steps
