@@ -83,6 +83,12 @@ FWD_SHAPES = [
     (512, 4400, 2, 2, "silu", False),
     (256, 10240, 2, 2, "gelu", False),
     (256, 300, 1, 2, "silu", False),
+    # exchange through global memory (N > 512) at its edges: a single step (nothing is published, no puller runs), two
+    # steps (one publication per tile), three tiles per cluster (flags, slot hand-over and their paired barriers cross
+    # tile boundaries, where a forward step is fed by TMA and not by a publication)
+    (1024, 2100, 1, 2, "tanh", False),
+    (1024, 2100, 2, 2, "silu", False),
+    (768, 4000, 4, 2, "tanh", False),
     # (relu is covered by the shapes above and by the benchmark-like cases below; with zero-mean random states many
     # pre-activations sit within bf16 rounding of relu's kink, where F' jumps between 0 and 1, so gradients of a
     # long random case differ from fp32 by a few percent in ANY bf16 implementation -- not a parity defect)
