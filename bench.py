@@ -42,12 +42,15 @@ WORKLOADS = {
     # forward-only rollout with the ideal cosine weights; decoded-angle error against the integrated target
     "c5": dict(N=120, B=65536, T=4000, act="tanh", max_av=0.1 * math.pi, cpu_slice=(1024, 200), rollout=True),
 }
-# DRAM bytes (read + write) per sample-timestep of each bf16-mode kernel at N=512, from the ncu captures summarised
-# under profiles/ (taken at T=64, B=4096; traffic is proportional to B*T).  None = no capture for that kernel/mode.
-NCU_CAPTURE_SOURCE = "ncu captures at T=64 summarised in profiles/{fwd,bwd}_tc_kernel_c3_T64.md, gemm_tc_kernel_dw_c3_T64.md"
+# DRAM bytes (read + write) per sample-timestep of each bf16-mode kernel, from the ncu captures summarised under
+# profiles/ (N=512: T=64, B=4096; N=1024: T=32, B=1024, a case of about the size of L2, so its write figures are a
+# lower bound; traffic is proportional to B*T).  None = no capture for that kernel/mode.
+NCU_CAPTURE_SOURCE = {512: "ncu captures at T=64 summarised in profiles/{fwd,bwd}_tc_kernel_c3_T64.md, gemm_tc_kernel_dw_c3_T64.md",
+                      1024: "ncu captures at T=32 summarised in profiles/{fwd,bwd}_tc_kernel_c4_T32.md (lower bound: part of the writes was still in L2)"}
 NCU_DRAM_BYTES_PER_SAMPLE_STEP = {
     ("bf16", 512): {"fwd_recurrent": (16.52e6 + 544.40e6) / (4096 * 64), "bwd_recurrent": (309.17e6 + 751.74e6) / (4096 * 64),
                     "dw_product": (1074.06e6 + 3.61e6) / (4096 * 64)},
+    ("bf16", 1024): {"fwd_recurrent": (13.56e6 + 96.37e6) / (1024 * 32), "bwd_recurrent": (83.09e6 + 147.29e6) / (1024 * 32)},
 }
 METRIC = "fwd+bwd sample-timesteps/s"
 UNIT = "sample-timesteps/s"
@@ -495,7 +498,7 @@ def run_ours(args, wl):
         traffic = cap * B_local * T / launches_per_step if cap is not None else None
         roof = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak, "traffic": traffic,
-                "traffic_source": NCU_CAPTURE_SOURCE if traffic is not None else None,
+                "traffic_source": NCU_CAPTURE_SOURCE.get(N) if traffic is not None else None,
                 "peak_source": f"{peak_src} ({'sustained' if sustained else 'burst'} bf16 GEMM)",
                 "ms_per_launch": ms_class / launches_per_step, "launches_per_step": launches_per_step,
                 "kernels_ms_per_step": {k: v[0] / args.steps for k, v in kern.items() if v[1] > 0},
