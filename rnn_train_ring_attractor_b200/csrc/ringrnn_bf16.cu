@@ -399,9 +399,10 @@ int bf16_backward_ckpt(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream
       prep_r0_kernel<<<296, 256, 0, s>>>(state0, p.B, p.N, l.BP, l.NP, Rh);
     }
     RINGRNN_CUDA_TRY(cudaGetLastError());
-    CUtensorMap tmR0, tmDL;
+    CUtensorMap tmR0, tmDL, tmDL32;
     if (!make_tmap_bf16_2d(&tmR0, Rh, (uint64_t)(Tc + 1) * l.BP, (uint64_t)l.NP, 128, 64) ||
-        !make_tmap_bf16_2d(&tmDL, DL, (uint64_t)Tc * l.BP, (uint64_t)bl.blocks * l.NP, 128, 64))
+        !make_tmap_bf16_2d(&tmDL, DL, (uint64_t)Tc * l.BP, (uint64_t)bl.blocks * l.NP, 128, 64) ||
+        !make_tmap_bf16_2d(&tmDL32, DL, (uint64_t)Tc * l.BP, (uint64_t)bl.blocks * l.NP, 32, 32, 64))
       return RINGRNN_ERR_CUDA;
 
     TcFwdParams fp;
@@ -441,7 +442,7 @@ int bf16_backward_ckpt(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream
     bp.status = status;
     bp.t0 = t0; bp.T_total = p.T;
     bp.carry_in = (c == n_ck - 1) ? nullptr : carry[(c + 1) & 1];
-    rc = tc_backward_launch(l.NP, l.pair, tmWb, tmDL, bp, s);
+    rc = tc_backward_launch(l.NP, l.pair, tmWb, tmDL, tmDL32, bp, s);
     if (rc != RINGRNN_OK) return rc;
 
     if (a.grad_A != nullptr) {
@@ -534,9 +535,11 @@ int bf16_backward(const RingRnnBwdArgs& a, const DevProblem& dp, cudaStream_t s)
   bp.dA_part = a.grad_A != nullptr ? dA_part : nullptr;
   bp.status = status;
   bp.t0 = 0; bp.T_total = p.T;
-  CUtensorMap tmDL;
-  if (!make_tmap_bf16_2d(&tmDL, DL, (uint64_t)p.T * l.BP, (uint64_t)bl.blocks * l.NP, 128, 64)) return RINGRNN_ERR_CUDA;
-  int rc = tc_backward_launch(l.NP, l.pair, tmW, tmDL, bp, s);
+  CUtensorMap tmDL, tmDL32;
+  if (!make_tmap_bf16_2d(&tmDL, DL, (uint64_t)p.T * l.BP, (uint64_t)bl.blocks * l.NP, 128, 64) ||
+      !make_tmap_bf16_2d(&tmDL32, DL, (uint64_t)p.T * l.BP, (uint64_t)bl.blocks * l.NP, 32, 32, 64))
+    return RINGRNN_ERR_CUDA;
+  int rc = tc_backward_launch(l.NP, l.pair, tmW, tmDL, tmDL32, bp, s);
   if (rc != RINGRNN_OK) return rc;
 
   if (a.grad_A != nullptr) {

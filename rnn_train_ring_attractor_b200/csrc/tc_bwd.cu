@@ -24,7 +24,8 @@ using namespace tcr;
 // carry is gathered over the groups, and DL gets one scaled copy of delta per active column.
 template <int NP, bool PAIR, bool GEN>
 __global__ void __launch_bounds__(THREADS, 1)
-bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmDL, const TcBwdParams p) {
+bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmDL,
+              const __grid_constant__ CUtensorMap tmDL32, const TcBwdParams p) {
   using C_ = Cfg<NP, PAIR>;
   static_assert(!GEN || (C_::ROUNDS == 1 && !PAIR), "weight groups: one K round, single CTAs");
   // Carry and delta arithmetic on packed fp32 pairs: fewer instructions, a few more registers.  It pays where the
@@ -39,6 +40,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   const Ctx<NP, PAIR> c = setup_cta<NP, PAIR>(smem_raw, p.dec_u, p.dec_v, p.N, p.status);
   const int ng = GEN ? p.ng : 1;
   const int dl_blocks = GEN ? 1 + p.n_act : 3;  // column blocks of NP in a row of DL
+  // The scaled copies of delta leave each epilogue warp's transposition buffer as one TMA store (store_rows_via_tma)
+  // or through shared-memory loads and global stores (store_rows_via_smem).  Measured, reverse kernel: TMA -3 % at
+  // N = 512, -8 % at N = 128, -2 % at N = 1024, but +5 % at N = 256, where the wait for the previous store's read of
+  // the one buffer is not hidden.
+  constexpr bool DL_BY_TMA = NP != 256;
   const uint32_t bars = c.bars, tmem_base = c.tmem_base;
   const WaitCtx& wctx = c.wctx;
   float* uv = c.uv;
@@ -74,6 +80,15 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     const bool want_dA = p.dA_part != nullptr;
     const int rq = (2 * q) / C_::SLOTS;  // the K round this CTA's own chunks belong to
     FreePhases<NP, PAIR> freed;
+    // the warp's 32 rows x 32 columns `o` to DL at (first column x, first row y)
+    auto store_copy = [&](const uint32_t* o, int x, int y) {
+      const uint32_t stage = c.stage_base + (uint32_t)(warp - 4) * 2048u;
+      if constexpr (DL_BY_TMA)
+        store_rows_via_tma(stage, lane, o, &tmDL32, x, y);
+      else
+        store_rows_via_smem(stage, lane, o, reinterpret_cast<uint8_t*>(p.DL + (size_t)y * ((size_t)dl_blocks * NP) + x),
+                            (size_t)dl_blocks * NP * 2);
+    };
     uint32_t g = 0;
     uint32_t n_sent = 0, sent_waited = 0;  // early publication: sends of own chunk 0 handed over / known complete
     uint32_t n_pub = 0;                    // exchange through global memory: publications of this CTA
@@ -201,37 +216,31 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       // scaled copies are formed from the bf16 delta the MMA sees, so the three blocks are consistent with one another;
       // packed bf16 multiplies (one instruction per two elements): the action scalar is rounded to bf16 first.
       auto dl_copies = [&](int t, int s, float Ls, float Rs, const uint32_t* packed) {
-        const uint32_t stage = c.stage_base + (uint32_t)(warp - 4) * 2048u;
-        const size_t dl_row_bytes = (size_t)3 * NP * 2;
-        // row 0 of this warp's 32-row block, first of this thread's 32 columns, column block 0
-        uint8_t* blk0 = reinterpret_cast<uint8_t*>(p.DL + ((size_t)t * p.BP + (b - lane)) * (3 * NP) + nq + 64 * s);
+        // row 0 of this warp's 32-row block, first of this thread's 32 columns within a column block
+        const int y0 = t * p.BP + (b - lane), x0 = nq + 64 * s;
         const uint32_t L2 = pack_bf16x2(Ls, Ls), R2 = pack_bf16x2(Rs, Rs);
         uint32_t o[16];
 #pragma unroll
         for (int w = 0; w < 16; ++w) o[w] = mul_bf16x2(packed[s * 16 + w], L2);
-        store_rows_via_smem(stage, lane, o, blk0 + (size_t)NP * 2, dl_row_bytes);
+        store_copy(o, NP + x0, y0);
 #pragma unroll
         for (int w = 0; w < 16; ++w) o[w] = mul_bf16x2(packed[s * 16 + w], R2);
-        store_rows_via_smem(stage, lane, o, blk0 + (size_t)2 * NP * 2, dl_row_bytes);
+        store_copy(o, 2 * NP + x0, y0);
       };
       // one scaled copy per active column (weight groups): block 1 + k = A[b,t,cols[k]] * delta_t
       auto dl_copies_generic = [&](int t, const uint32_t* packed) {
-        const uint32_t stage = c.stage_base + (uint32_t)(warp - 4) * 2048u;
-        const size_t dl_row_bytes = (size_t)dl_blocks * NP * 2;
         const float* at = p.A + ((size_t)b * p.T_total + p.t0 + t) * p.a_dim;
         for (int k = 0; k < p.n_act; ++k) {
           const float ak = valid ? __ldg(at + p.cols[k]) : 0.f;
 #pragma unroll
           for (int s = 0; s < 2; ++s) {
-            uint8_t* blk0 = reinterpret_cast<uint8_t*>(p.DL + ((size_t)t * p.BP + (b - lane)) * ((size_t)dl_blocks * NP) +
-                                                       nq + 64 * s);
             uint32_t o[16];
 #pragma unroll
             for (int w = 0; w < 16; ++w) {
               const uint32_t d2 = packed[s * 16 + w];
               o[w] = pack_bf16x2(ak * bf16_lo(d2), ak * bf16_hi(d2));
             }
-            store_rows_via_smem(stage, lane, o, blk0 + (size_t)(1 + k) * NP * 2, dl_row_bytes);
+            store_copy(o, (1 + k) * NP + nq + 64 * s, t * p.BP + (b - lane));
           }
         }
       };
@@ -349,26 +358,24 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (warp == 4 && lane == 0) RINGRNN_STAMP(g, 12);
         // off the critical path: [delta | L*delta | R*delta] for the weight-gradient GEMM.  The scaled copies are
         // formed from the bf16 delta the MMA sees, so the three blocks are consistent with one another.
-        const uint32_t stage = c.stage_base + (uint32_t)(warp - 4) * 2048u;
-        const size_t dl_row_bytes = (size_t)dl_blocks * NP * 2;
         if constexpr (!GEN) {
           // packed bf16 multiplies (one instruction per two elements): the action scalar is rounded to bf16 first
 #pragma unroll
           for (int s = 0; s < 2; ++s) {
-            // row 0 of this warp's 32-row block, first of this thread's 32 columns, column block 0
-            uint8_t* blk0 = reinterpret_cast<uint8_t*>(p.DL + ((size_t)t * p.BP + (b - lane)) * (3 * NP) + nq + 64 * s);
+            // row 0 of this warp's 32-row block, first of this thread's 32 columns within a column block
+            const int y0 = t * p.BP + (b - lane), x0 = nq + 64 * s;
             const uint32_t L2 = pack_bf16x2(L, L), R2 = pack_bf16x2(R, R);
             uint32_t o[16];
 #pragma unroll
             for (int w = 0; w < 16; ++w) {
               o[w] = mul_bf16x2(packed[s * 16 + w], L2);
             }
-            store_rows_via_smem(stage, lane, o, blk0 + (size_t)NP * 2, dl_row_bytes);
+            store_copy(o, NP + x0, y0);
 #pragma unroll
             for (int w = 0; w < 16; ++w) {
               o[w] = mul_bf16x2(packed[s * 16 + w], R2);
             }
-            store_rows_via_smem(stage, lane, o, blk0 + (size_t)2 * NP * 2, dl_row_bytes);
+            store_copy(o, 2 * NP + x0, y0);
           }
         } else {
           // one scaled copy per active column: block 1 + k = A[b,t,cols[k]] * delta_t
@@ -377,15 +384,13 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             const float ak = valid ? __ldg(at + p.cols[k]) : 0.f;
 #pragma unroll
             for (int s = 0; s < 2; ++s) {
-              uint8_t* blk0 = reinterpret_cast<uint8_t*>(p.DL + ((size_t)t * p.BP + (b - lane)) * ((size_t)dl_blocks * NP) +
-                                                         nq + 64 * s);
               uint32_t o[16];
 #pragma unroll
               for (int w = 0; w < 16; ++w) {
                 const uint32_t d2 = packed[s * 16 + w];
                 o[w] = pack_bf16x2(ak * bf16_lo(d2), ak * bf16_hi(d2));
               }
-              store_rows_via_smem(stage, lane, o, blk0 + (size_t)(1 + k) * NP * 2, dl_row_bytes);
+              store_copy(o, (1 + k) * NP + nq + 64 * s, t * p.BP + (b - lane));
             }
           }
         }
@@ -583,13 +588,14 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       }
     }
     if (EARLY && stop) named_bar_arrive(SENDER_BAR, SENDER_BAR_THREADS);  // a sender waiting for the next chunk 0 is let go
-    if (warp == 4 && lane == 0) bulk_wait_all<0>();  // the delta stores have left shared memory and landed
+    if (lane == 0) bulk_wait_all<0>();  // this warp's stores (delta chunks, scaled copies) have left shared memory and landed
   }
   teardown_cta<NP, PAIR>(c);
 }
 
 template <int NP, bool PAIR, bool GEN = false>
-static int launch_bwd_tc(const CUtensorMap& tmW, const CUtensorMap& tmDL, const TcBwdParams& p, cudaStream_t s) {
+static int launch_bwd_tc(const CUtensorMap& tmW, const CUtensorMap& tmDL, const CUtensorMap& tmDL32, const TcBwdParams& p,
+                         cudaStream_t s) {
   using C_ = Cfg<NP, PAIR>;
   auto kernel = bwd_tc_kernel<NP, PAIR, GEN>;
   RINGRNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::SMEM));
@@ -609,24 +615,25 @@ static int launch_bwd_tc(const CUtensorMap& tmW, const CUtensorMap& tmDL, const 
   cfg.gridDim = dim3(n_clusters * C_::CL, 1, 1);
   {
     LaunchScope ls(K_BWD, s);
-    RINGRNN_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmW, tmDL, p));
+    RINGRNN_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmW, tmDL, tmDL32, p));
   }
   return RINGRNN_OK;
 }
 
-int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmDL, const TcBwdParams& p,
+int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmDL, const CUtensorMap& tmDL32,
+                       const TcBwdParams& p,
                        cudaStream_t s) {
   if (p.ng > 1) {  // more than two active action columns
     if (pair) return RINGRNN_ERR_UNSUPPORTED;
-    if (NP == 128) return launch_bwd_tc<128, false, true>(tmW, tmDL, p, s);
-    if (NP == 256) return launch_bwd_tc<256, false, true>(tmW, tmDL, p, s);
-    if (NP == 512) return launch_bwd_tc<512, false, true>(tmW, tmDL, p, s);
+    if (NP == 128) return launch_bwd_tc<128, false, true>(tmW, tmDL, tmDL32, p, s);
+    if (NP == 256) return launch_bwd_tc<256, false, true>(tmW, tmDL, tmDL32, p, s);
+    if (NP == 512) return launch_bwd_tc<512, false, true>(tmW, tmDL, tmDL32, p, s);
     return RINGRNN_ERR_UNSUPPORTED;
   }
-  if (NP == 128) return pair ? launch_bwd_tc<128, true>(tmW, tmDL, p, s) : launch_bwd_tc<128, false>(tmW, tmDL, p, s);
-  if (NP == 256) return pair ? launch_bwd_tc<256, true>(tmW, tmDL, p, s) : launch_bwd_tc<256, false>(tmW, tmDL, p, s);
-  if (NP == 512) return pair ? launch_bwd_tc<512, true>(tmW, tmDL, p, s) : launch_bwd_tc<512, false>(tmW, tmDL, p, s);
-  if (NP == 1024 && !pair) return launch_bwd_tc<1024, false>(tmW, tmDL, p, s);  // two K rounds per step, clusters of 8
+  if (NP == 128) return pair ? launch_bwd_tc<128, true>(tmW, tmDL, tmDL32, p, s) : launch_bwd_tc<128, false>(tmW, tmDL, tmDL32, p, s);
+  if (NP == 256) return pair ? launch_bwd_tc<256, true>(tmW, tmDL, tmDL32, p, s) : launch_bwd_tc<256, false>(tmW, tmDL, tmDL32, p, s);
+  if (NP == 512) return pair ? launch_bwd_tc<512, true>(tmW, tmDL, tmDL32, p, s) : launch_bwd_tc<512, false>(tmW, tmDL, tmDL32, p, s);
+  if (NP == 1024 && !pair) return launch_bwd_tc<1024, false>(tmW, tmDL, tmDL32, p, s);  // two K rounds per step, clusters of 8
   return RINGRNN_ERR_UNSUPPORTED;
 }
 

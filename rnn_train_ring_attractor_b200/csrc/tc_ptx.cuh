@@ -411,7 +411,8 @@ __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t k) {
 // ---- host: tensor maps ------------------------------------------------------------------------------
 // 2-D bf16 row-major tensor [rows, cols] (cols contiguous), box = [box_rows, box_cols], 128-byte swizzle.
 // Returns false if the driver entry point is unavailable or the encode fails.
+// box_cols * 2 bytes must not exceed the swizzle span (128 or 64 bytes)
 bool make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                       uint32_t box_cols);
+                       uint32_t box_cols, int swizzle_bytes = 128);
 
 }  // namespace ringrnn

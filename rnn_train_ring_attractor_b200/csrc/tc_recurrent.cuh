@@ -119,8 +119,10 @@ struct TcBwdParams {
 // `generic`: more than two active action columns (p.ng > 1 weight groups); NP <= 512, no CTA pairs
 int tc_forward_launch(int act, int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmR0, const TcFwdParams& p,
                       cudaStream_t s);
-int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmDL, const TcBwdParams& p,
-                       cudaStream_t s);
+// tmDL: DL with a [128 rows x 64 columns] box (128-byte swizzle: the delta chunks); tmDL32: the same tensor with a
+// [32 x 32] box (64-byte swizzle: the scaled copies, one store per epilogue warp)
+int tc_backward_launch(int NP, bool pair, const CUtensorMap& tmW, const CUtensorMap& tmDL, const CUtensorMap& tmDL32,
+                       const TcBwdParams& p, cudaStream_t s);
 
 namespace tcr {
 
@@ -1000,6 +1002,8 @@ __device__ __forceinline__ bool publish_global(const Ctx<NP, PAIR>& c, const uin
   // through the warp's transposition buffer: a store instruction then covers 8 rows x 64 bytes instead of 32 rows x
   // 16 bytes (the direct form kept the load/store unit busy for 1.3-2.8 K cycles per publication)
   const uint32_t stage = c.stage_base + (uint32_t)(warp - 4) * 2048u;
+  if (lane == 0) bulk_wait_read<0>();  // (reverse kernel) a TMA store of the scaled copies may still be reading the buffer
+  __syncwarp();
 #pragma unroll
   for (int s = 0; s < 2; ++s)
     store_rows_via_smem<false>(stage, lane, packed + 16 * s,
@@ -1120,6 +1124,31 @@ __device__ __forceinline__ void store_rows_via_smem(uint32_t stage, int lane, co
     else *reinterpret_cast<uint4*>(dst) = make_uint4(a, b, c2, d);
   }
   __syncwarp();
+}
+
+// The same 32 rows x 64 bytes as ONE TMA store out of the warp's buffer (a [32 rows x 32 columns] box in the 64-byte
+// swizzle, which is the arrangement the buffer is written in): no shared-memory loads and no global store instructions
+// in the epilogue threads.  `tm` maps the row-major destination with that box; (x, y) = first column, first row.
+// Lane 0 issues the store and, before the buffer is written again, waits until the previous one has read it; at the
+// end of the kernel it must wait for its stores to complete (bulk_wait_all).
+__device__ __forceinline__ void store_rows_via_tma(uint32_t stage, int lane, const uint32_t* w16, const CUtensorMap* tm,
+                                                   int x, int y) {
+  if (lane == 0) tc::bulk_wait_read<0>();
+  __syncwarp();
+  const uint32_t sw = ((uint32_t)lane >> 1) & 3u;
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const uint32_t addr = stage + lane * 64 + (((uint32_t)v ^ sw) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w16[4 * v]), "r"(w16[4 * v + 1]),
+                 "r"(w16[4 * v + 2]), "r"(w16[4 * v + 3])
+                 : "memory");
+  }
+  tc::fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tc::tma_store_2d(tm, stage, x, y);
+    tc::bulk_commit();
+  }
 }
 
 }  // namespace tcr
