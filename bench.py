@@ -48,8 +48,8 @@ WORKLOADS = {
 NCU_CAPTURE_SOURCE = {512: "ncu captures at T=64 summarised in profiles/{fwd,bwd}_tc_kernel_c3_T64.md, gemm_tc_kernel_dw_c3_T64.md",
                       1024: "ncu captures at T=32 summarised in profiles/{fwd,bwd}_tc_kernel_c4_T32.md (lower bound: part of the writes was still in L2)"}
 NCU_DRAM_BYTES_PER_SAMPLE_STEP = {
-    ("bf16", 512): {"fwd_recurrent": (16.52e6 + 544.40e6) / (4096 * 64), "bwd_recurrent": (309.17e6 + 751.74e6) / (4096 * 64),
-                    "dw_product": (1074.06e6 + 3.61e6) / (4096 * 64)},
+    ("bf16", 512): {"fwd_recurrent": (16.50e6 + 545.05e6) / (4096 * 64), "bwd_recurrent": (309.09e6 + 751.43e6) / (4096 * 64),
+                    "dw_product": (1073.80e6 + 4.66e6) / (4096 * 64)},
     ("bf16", 1024): {"fwd_recurrent": (13.56e6 + 96.37e6) / (1024 * 32), "bwd_recurrent": (83.09e6 + 147.29e6) / (1024 * 32)},
 }
 METRIC = "fwd+bwd sample-timesteps/s"
