@@ -58,7 +58,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   if (warp < 4) {
     reg_dec<LOW_REGS>();
     if (warp == 0 && lane == 0) {
+#ifdef RINGRNN_NO_SPLIT
       producer_loop<NP, PAIR, GEN>(c, &tmW, total_steps, 302, ng);
+#else
+      producer_loop<NP, PAIR, GEN, EARLY>(c, &tmW, total_steps, 302, ng);
+#endif
     } else if (warp == 1 && lane == 0) {
       if (c.leader) mma_loop<NP, PAIR, false, GEN>(c, total_steps, T, 310, true, ng);
     } else if (warp == 2 && lane == 0) {

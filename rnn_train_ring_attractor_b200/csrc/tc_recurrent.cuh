@@ -476,8 +476,8 @@ __device__ __forceinline__ void teardown_cta(const Ctx<NP, PAIR>& c) {
 
 // Weight stream (one thread per CTA).  Tile order per step: round by round, sub-slice 0 then 1, within a sub-slice
 // the `ng` weight groups one after the other, the slots starting at this slice's own.
-// SPLIT (forward with early publication): the tiles of the even slots come first, for both sub-slices, then those of
-// the odd slots -- the order in which mma_loop consumes them.
+// SPLIT (early publication): the tiles of the even slots come first, for both sub-slices, then those of the odd
+// slots -- the order in which mma_loop consumes them.
 template <int NP, bool PAIR, bool GEN = false, bool SPLIT = false>
 __device__ __forceinline__ void producer_loop(const Ctx<NP, PAIR>& c, const CUtensorMap* tmW, uint32_t total_steps,
                                               int code, int ng_arg = 1) {
@@ -547,12 +547,11 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
   using namespace tc;
   constexpr int KC = C_::KC, NS = C_::NS, SL = C_::SLOTS, R = C_::ROUNDS;
   constexpr uint32_t idesc = make_idesc_bf16(PAIR ? 256 : 128, C_::RB, 0, 0);
-  constexpr bool EARLY_FWD = FWD && !GEN && C_::EARLY;
   constexpr bool EARLY_ANY = !GEN && C_::EARLY && (FWD || NP >= 512);  // as the kernels' own EARLY flags
 #ifdef RINGRNN_NO_SPLIT
   constexpr bool SPLIT = false;
 #else
-  constexpr bool SPLIT = EARLY_FWD;
+  constexpr bool SPLIT = EARLY_ANY;
 #endif
   const int rot = (2 * c.q) % SL, rq = (2 * c.q) / SL;
   uint32_t ph = 0, npub = 0;
@@ -572,12 +571,14 @@ __device__ __forceinline__ void mma_loop(const Ctx<NP, PAIR>& c, uint32_t total_
     long long acc_w = 0, acc_a = 0, acc_p = 0, t0;
 #endif
     if constexpr (SPLIT) {
-      // Split schedule (forward with early publication).  The chunks in the even slots -- chunk 0 of every slice -- are
-      // published while the epilogue of sub-slice 1 is still running, so their share of the next step's MMAs, for both
-      // accumulators, is issued first and overlaps that epilogue; the odd slots follow once chunk 1 has arrived.
-      // Accumulator s is complete after the odd half of sub-slice s.
+      // Split schedule (with early publication, both directions).  The chunks in the even slots -- chunk 0 of every
+      // slice -- are published while the epilogue of sub-slice 1 is still running, so their share of the next step's
+      // MMAs, for both accumulators, is issued first and overlaps that epilogue; the odd slots follow once chunk 1 has
+      // arrived.  Accumulator s is complete after the odd half of sub-slice s.  (In the reverse kernel this pays only
+      // since the scaled copies of delta leave the epilogue as TMA stores: -3 % at N = 512; before, the epilogue of
+      // sub-slice 0, no longer hidden behind a whole pass, cost as much as the overlap gained.)
       const int next_t = (t + 1 == T) ? 0 : t + 1;
-      const bool next_by_copy = next_t != 0;
+      const bool next_by_copy = FWD ? next_t != 0 : g + 1 < total_steps;
       for (int half = 0; half < 2; ++half) {
         for (int s = 0; s < 2; ++s) {
           if (half == 0) {
