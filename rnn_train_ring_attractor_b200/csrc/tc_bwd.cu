@@ -28,10 +28,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               const __grid_constant__ CUtensorMap tmDL32, const TcBwdParams p) {
   using C_ = Cfg<NP, PAIR>;
   static_assert(!GEN || (C_::ROUNDS == 1 && !PAIR), "weight groups: one K round, single CTAs");
-  // Carry and delta arithmetic on packed fp32 pairs: fewer instructions, a few more registers.  It pays where the
-  // epilogue is the longer part of a step (measured: -9 % at N = 256, -8 % at N = 128) and costs 1.5 % at N = 512,
-  // where this kernel sits at its register limit.
-  constexpr bool PACKED = NP <= 256;
+  // Carry and delta arithmetic on packed fp32 pairs: fewer instructions, a few more registers (measured: -9 % at
+  // N = 256, -8 % at N = 128; at N = 512 it cost 1.5 % while the scaled copies still went through shared-memory loads
+  // and global stores, and gains 1.7 % now that they leave as TMA stores).
+  constexpr bool PACKED = true;
   // delta of sub-slice 0 is published while accumulator 1 is still being filled (see Cfg::EARLY and sender_loop).
   // Measured at N = 512 (cluster of 4): -4.5 % on this kernel; at N = 256 (cluster of 2, half the exchange, a step a
   // third as long) the extra hand-over costs more than the overlap gains (+6 %), so it stays off there.
